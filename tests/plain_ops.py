@@ -277,6 +277,206 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
         logits[r, t] = v
 
 
+# ---- blocks with norms on both sides, scaled rotary tables, general attention, recurrent mixers -----
+def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dtype, rows=None):
+    """x += mult * rms(y) * post_weight;  out = rms(x) * weight (for `rows` only, x untouched)."""
+    yf = _f(y)
+    add = mult * (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + post_eps) * post_weight)
+    if rows is None:
+        x += add
+        src = x
+    else:
+        src = x[rows.long()] + add[rows.long()]
+    if weight is None:
+        return None
+    return (src * torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+
+def gated_group_rmsnorm(y, z, weight, eps, group, gate_first, out_dtype):
+    n, width = y.shape
+    zf = _f(z)
+    gate = zf / (1.0 + torch.exp(-zf))
+    w = weight.repeat(width // weight.numel())
+    v = y * gate if gate_first else y
+    v = v.view(n, width // group, group)
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).view(n, width) * w
+    return (v if gate_first else v * gate).to(out_dtype)
+
+
+def scale_rows(x, factor):
+    x *= factor
+    return x
+
+
+def rope_cos_sin_scaled(positions, freq, mult):
+    ang = positions.to(torch.float32)[:, None] * freq[None, :]
+    return torch.cos(ang) * mult, torch.sin(ang) * mult
+
+
+def qk_norm_rope_write_split(qkv, nh, nkv, dk, dv, q_weight, k_weight, eps, cos, sin, rot, interleaved, cache_layer,
+                             page_size, slot_mapping, status=None):
+    n = qkv.shape[0]
+    for t in range(n):
+        for h in range(nh + 2 * nkv):
+            is_q, is_k = h < nh, nh <= h < nh + nkv
+            if is_q or is_k:
+                c0, d = h * dk, dk
+            else:
+                c0, d = (nh + nkv) * dk + (h - nh - nkv) * dv, dv
+            v = _f(qkv[t, c0:c0 + d]).clone()
+            w = q_weight if is_q else (k_weight if is_k else None)
+            if w is not None:
+                v = v * torch.rsqrt(v.pow(2).mean() + eps) * w
+            if (is_q or is_k) and cos is not None:
+                half = rot // 2
+                r = v.clone()
+                for i in range(half):
+                    a, b = (2 * i, 2 * i + 1) if interleaved else (i, i + half)
+                    r[a] = v[a] * cos[t, i] - v[b] * sin[t, i]
+                    r[b] = v[b] * cos[t, i] + v[a] * sin[t, i]
+                v = r
+            if is_q:
+                qkv[t, c0:c0 + d] = v.to(qkv.dtype)
+            elif cache_layer is not None:
+                slot = int(slot_mapping[t])
+                pg, off = slot // page_size, slot % page_size
+                if is_k:
+                    e0 = ((h - nh) * page_size + off) * dk
+                else:
+                    e0 = nkv * page_size * dk + ((h - nh - nkv) * page_size + off) * dv
+                cache_layer[pg, e0:e0 + d] = v.to(cache_layer.dtype)
+
+
+def masked_attention_splits(num_seqs, max_q, max_k, nh, nkv):
+    return 1
+
+
+def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k,
+                     nh, nkv, dk, dv, scale, *, window=0, chunk=0, sinks=None, gate=None, splits=None, status=None):
+    rep = nh // nkv
+    out = torch.zeros((n, nh * dv), dtype=torch.float32)
+    kpart = nkv * page_size * dk
+    for s in range(num_seqs):
+        q0, q1, klen = int(cu_q[s]), int(cu_q[s + 1]), int(seqlens_k[s])
+        qlen = q1 - q0
+        for j in range(qlen):
+            p = klen - qlen + j
+            lo = 0
+            if window > 0:
+                lo = max(lo, p - window + 1)
+            if chunk > 0:
+                lo = max(lo, (p // chunk) * chunk)
+            for h in range(nh):
+                g = h // rep
+                qv = _f(q[q0 + j, h * dk:(h + 1) * dk])
+                ks, vs = [], []
+                for i in range(lo, p + 1):
+                    pg, off = int(block_table[s, i // page_size]), i % page_size
+                    ks.append(_f(cache_layer[pg, (g * page_size + off) * dk:(g * page_size + off + 1) * dk]))
+                    vs.append(_f(cache_layer[pg, kpart + (g * page_size + off) * dv:kpart + (g * page_size + off + 1) * dv]))
+                sc = torch.stack(ks) @ qv * scale
+                mx = sc.max()
+                if sinks is not None:
+                    mx = torch.maximum(mx, sinks[h])
+                e = torch.exp(sc - mx)
+                den = e.sum() + (torch.exp(sinks[h] - mx) if sinks is not None else 0.0)
+                o = (e / den) @ torch.stack(vs)
+                if gate is not None:
+                    o = o * torch.sigmoid(_f(gate[q0 + j, h]))
+                out[q0 + j, h * dv:(h + 1) * dv] = o
+    return out.to(q.dtype)
+
+
+def causal_conv_silu(x, taps, bias, state, state_slots, tok_seq, cu_q, positions, max_q, status=None):
+    n, C = x.shape
+    L = taps.shape[0]
+    out = torch.zeros((n, C), dtype=torch.float32)
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        p0, slot = int(positions[r0]), int(state_slots[s])
+        hist = []
+        for j in range(L - 1):
+            pos = p0 - (L - 1) + j
+            hist.append(state[slot, j * C:(j + 1) * C].clone() if pos >= 0 else torch.zeros(C))
+        for r in range(r0, r1):
+            hist.append(_f(x[r]))
+            acc = torch.zeros(C) if bias is None else bias.clone()
+            for k in range(L):
+                acc = acc + taps[k] * hist[len(hist) - L + k]
+            out[r] = acc / (1.0 + torch.exp(-acc))
+            hist = hist[-(L - 1):] if L > 1 else []
+        for j in range(L - 1):
+            state[slot, j * C:(j + 1) * C] = hist[j]
+    return out.to(x.dtype)
+
+
+def _softplus(z):
+    return torch.where(z > 20.0, z, torch.log1p(torch.exp(torch.clamp(z, max=20.0))))
+
+
+def gated_delta(qkv, ab, A_log, dt_bias, state, state_offset, state_slots, cu_q, positions, nh, nkv, dk, dv,
+                norm_eps=1e-6, status=None):
+    n = qkv.shape[0]
+    out = torch.zeros((n, nh * dv), dtype=torch.float32)
+    rep = nh // nkv
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        slot = int(state_slots[s])
+        S = state[slot, state_offset:state_offset + nh * dk * dv].view(nh, dk, dv).clone()
+        if int(positions[r0]) == 0:
+            S.zero_()
+        for r in range(r0, r1):
+            row = _f(qkv[r])
+            for h in range(nh):
+                g = h // rep
+                qv = row[g * dk:(g + 1) * dk]
+                kv = row[nkv * dk + g * dk:nkv * dk + (g + 1) * dk]
+                vv = row[2 * nkv * dk + h * dv:2 * nkv * dk + (h + 1) * dv]
+                qv = qv * torch.rsqrt(qv.pow(2).sum() + norm_eps) * dk ** -0.5
+                kv = kv * torch.rsqrt(kv.pow(2).sum() + norm_eps)
+                beta = torch.sigmoid(_f(ab[r, nh + h]))
+                dec = torch.exp(-torch.exp(A_log[h]) * _softplus(_f(ab[r, h]) + dt_bias[h]))
+                S[h] = dec * S[h]
+                u = beta * (vv - S[h].t() @ kv)
+                S[h] = S[h] + torch.outer(kv, u)
+                out[r, h * dv:(h + 1) * dv] = S[h].t() @ qv
+        state[slot, state_offset:state_offset + nh * dk * dv] = S.reshape(-1)
+    return out
+
+
+def state_space(xbc, dt, A_log, dt_bias, D, state, state_offset, state_slots, cu_q, positions, nh, groups, n_state, head,
+                status=None):
+    n = xbc.shape[0]
+    out = torch.zeros((n, nh * head), dtype=torch.float32)
+    rep = nh // groups
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        slot = int(state_slots[s])
+        S = state[slot, state_offset:state_offset + nh * n_state * head].view(nh, n_state, head).clone()
+        if int(positions[r0]) == 0:
+            S.zero_()
+        for r in range(r0, r1):
+            row = _f(xbc[r])
+            for h in range(nh):
+                g = h // rep
+                xv = row[h * head:(h + 1) * head]
+                Bv = row[nh * head + g * n_state:nh * head + (g + 1) * n_state]
+                Cv = row[nh * head + groups * n_state + g * n_state:nh * head + groups * n_state + (g + 1) * n_state]
+                step = _softplus(_f(dt[r, h]) + dt_bias[h])
+                S[h] = torch.exp(-torch.exp(A_log[h]) * step) * S[h] + step * torch.outer(Bv, xv)
+                out[r, h * head:(h + 1) * head] = S[h].t() @ Cv + D[h] * xv
+        state[slot, state_offset:state_offset + nh * n_state * head] = S.reshape(-1)
+    return out
+
+
 ALL = ["embed", "resolve_tokens", "sample_truncated", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
-       "apply_penalties"]
+       "apply_penalties", "postnorm_add_rmsnorm", "gated_group_rmsnorm", "scale_rows", "rope_cos_sin_scaled",
+       "qk_norm_rope_write_split", "masked_attention_splits", "masked_attention", "causal_conv_silu", "gated_delta",
+       "state_space"]

@@ -87,6 +87,11 @@ def resolve_architecture(v: Dict[str, Any]) -> Architecture:
         tried.append(archs[0])
         if archs[0] in _REGISTRY:
             return _REGISTRY[archs[0]]
+    one = v.get("architecture")                 # some configurations name a single architecture
+    if isinstance(one, str):
+        tried.append(one)
+        if one in _REGISTRY:
+            return _REGISTRY[one]
     mt = v.get("model_type")
     if isinstance(mt, str):
         tried.append(mt)
@@ -149,4 +154,4 @@ def _ensure_builtin() -> None:
 
 
 #: modules that ship with the package and register an architecture when imported
-BUILTIN_ARCHITECTURE_MODULES = ["vapi_b200.models.lfm2"]
+BUILTIN_ARCHITECTURE_MODULES = ["vapi_b200.models.lfm2", "vapi_b200.models.vukavik"]

@@ -379,4 +379,144 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
     return check_launch("swiglu", e);
 }
 
+
+// A sublayer's output y, normed on its way into the stream, and the norm that reads the stream
+// next, in one pass over the row:
+//   x <- x + mult * (y * rsqrt(mean(y^2) + eps_post) * w_post);   out = x * rsqrt(mean(x^2) + eps) * w
+// (blocks that norm a sublayer on both sides and scale its contribution).  `w` null: only the
+// stream is updated.  With `rows` the output has one row per entry and x is left untouched.
+// One block per row; every sum is float.
+template <typename T>
+__global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ y,
+                                            const float* __restrict__ w_post, float eps_post, float mult,
+                                            const float* __restrict__ w, float eps,
+                                            const int* __restrict__ rows, T* __restrict__ out,
+                                            int n_out, int hidden, int write_x) {
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (j >= n_out) return;
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * hidden;
+    const T* yr = y + (size_t)row * hidden;
+    float ssy = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = to_f32(yr[c]);
+        ssy += v * v;
+    }
+    ssy = block_sum(ssy, red);
+    const float inv_y = rsqrtf(ssy / (float)hidden + eps_post);
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
+        if (write_x) xr[c] = v;
+        ss += v * v;
+    }
+    if (!w) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    T* orow = out + (size_t)j * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        // each thread reads back what it wrote itself
+        const float v = write_x ? xr[c] : xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
+        orow[c] = from_f32<T>(v * inv * w[c]);
+    }
+}
+
+VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, const float* w_post, float eps_post,
+                                          float mult, const float* w, float eps, const int* rows, void* out,
+                                          int n_out, int hidden, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (hidden <= 0 || !w_post) return fail(-1, "postnorm_add_rmsnorm: hidden=%d or no weight", hidden);
+    if (w && !out) return fail(-1, "postnorm_add_rmsnorm: a following norm needs an output");
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const int write_x = rows ? 0 : 1;
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(postnorm_add_rmsnorm_kernel<float>, n_out, threads, 0, stream, x, (const float*)y, w_post, eps_post, mult,
+                   w, eps, rows, (float*)out, n_out, hidden, write_x);
+    else if (dtype == VAPI_BF16)
+        e = launch(postnorm_add_rmsnorm_kernel<__nv_bfloat16>, n_out, threads, 0, stream, x, (const __nv_bfloat16*)y, w_post,
+                   eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+    else
+        return fail(-2, "postnorm_add_rmsnorm: unsupported dtype %d", dtype);
+    return check_launch("postnorm_add_rmsnorm", e);
+}
+
+// RMS norm over equal groups of a row, with a gate:  out = norm_g(y) * w * silu(z)  (gate_first 0)
+// or  out = norm_g(y * silu(z)) * w  (gate_first 1).  y is float [n, width] (what a recurrence
+// left), z is T with its own row stride, w has w_len elements and is indexed by column % w_len (one
+// weight per head size, or one per column).  One warp per (row, group).
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
+                                           const float* __restrict__ w, int w_len, float eps, int gate_first,
+                                           T* __restrict__ out, int n, int width, int group) {
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
+    const int groups = width / group;
+    if (item >= (long long)n * groups) return;
+    const int t = (int)(item / groups), g = (int)(item - (long long)t * groups);
+    const float* yr = y + (size_t)t * width + (size_t)g * group;
+    const T* zr = z + (size_t)t * z_stride + (size_t)g * group;
+    float ss = 0.f;
+    for (int c = lane; c < group; c += 32) {
+        float v = yr[c];
+        if (gate_first) {
+            const float zv = to_f32(zr[c]);
+            v *= zv / (1.f + expf(-zv));
+        }
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)group + eps);
+    T* orow = out + (size_t)t * width + (size_t)g * group;
+    for (int c = lane; c < group; c += 32) {
+        const float zv = to_f32(zr[c]);
+        const float gate = zv / (1.f + expf(-zv));
+        const float wv = w[(g * group + c) % w_len];
+        const float v = gate_first ? (yr[c] * gate) * inv * wv : yr[c] * inv * wv * gate;
+        orow[c] = from_f32<T>(v);
+    }
+}
+
+VAPI_EXPORT int vapi_gated_group_rmsnorm(const float* y, const void* z, long long z_stride, int dtype, const float* w,
+                                         int w_len, float eps, int gate_first, void* out, int n, int width, int group,
+                                         cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (width <= 0 || group <= 0 || width % group || w_len <= 0)
+        return fail(-1, "gated_group_rmsnorm: width %d, group %d, weight %d", width, group, w_len);
+    const long long items = (long long)n * (width / group);
+    const int warps = 4;
+    const int blocks = (int)((items + warps - 1) / warps);
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(gated_group_rmsnorm_kernel<float>, blocks, warps * 32, 0, stream, y, (const float*)z, z_stride, w, w_len, eps,
+                   gate_first, (float*)out, n, width, group);
+    else if (dtype == VAPI_BF16)
+        e = launch(gated_group_rmsnorm_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, y, (const __nv_bfloat16*)z, z_stride,
+                   w, w_len, eps, gate_first, (__nv_bfloat16*)out, n, width, group);
+    else
+        return fail(-2, "gated_group_rmsnorm: unsupported dtype %d", dtype);
+    return check_launch("gated_group_rmsnorm", e);
+}
+
+// x *= factor (the output head of a model that scales its logits)
+__global__ void scale_kernel(float* __restrict__ x, float factor, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_trigger();
+    pdl_wait();
+    for (; i < total; i += stride) x[i] *= factor;
+}
+
+VAPI_EXPORT int vapi_scale(float* x, float factor, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    long long blocks = (total + 255) / 256;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    return check_launch("scale", launch(scale_kernel, (int)blocks, 256, 0, stream, x, factor, (size_t)total));
+}
+
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

@@ -287,4 +287,133 @@ VAPI_EXPORT int vapi_qk_norm_rope_write(void* qkv, int dtype, const float* qw, c
     return check_launch("qk_norm_rope_write", e);
 }
 
+
+// cos/sin rows from per-pair frequencies that the host has already scaled (a frequency
+// interpolation such as YaRN changes the frequencies and multiplies both tables by one number).
+__global__ void rope_cos_sin_scaled_kernel(const int* __restrict__ positions, const float* __restrict__ freq,
+                                           float mult, float* __restrict__ cosr, float* __restrict__ sinr,
+                                           int n, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= n * half) return;
+    const int t = i / half, j = i - t * half;
+    const float a = (float)positions[t] * freq[j];
+    cosr[i] = cosf(a) * mult;
+    sinr[i] = sinf(a) * mult;
+}
+
+VAPI_EXPORT int vapi_rope_cos_sin_scaled(const int* positions, const float* freq, float mult, float* cosr,
+                                         float* sinr, int n, int half, cudaStream_t stream) {
+    if (n <= 0 || half <= 0) return 0;
+    const int total = n * half;
+    return check_launch("rope_cos_sin_scaled", launch(rope_cos_sin_scaled_kernel, (total + 255) / 256, 256, 0, stream,
+                                                        positions, freq, mult, cosr, sinr, n, half));
+}
+
+// The general form of the kernel above: keys of width dk and values of width dv in a row
+// [q heads x dk | k heads x dk | v heads x dv | anything else] of `row_stride` elements; the rotation
+// pairs either (i, i + rot/2) (rotate-half) or (2i, 2i+1) (interleaved) over the first `rot`
+// elements of a head; a cache page holds the keys [nkv, page_size, dk] and then the values
+// [nkv, page_size, dv].  One warp per (token, head).
+template <typename T>
+__global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ qw,
+                                                const float* __restrict__ kw, float eps,
+                                                const float* __restrict__ cosr, const float* __restrict__ sinr,
+                                                int rot, int interleaved, T* __restrict__ cache,
+                                                const int* __restrict__ slot_mapping, int n, int nh, int nkv,
+                                                int dk, int dv, int page_size, int num_pages,
+                                                int* __restrict__ status) {
+    __shared__ float sh[QK_WARPS][QK_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+    pdl_trigger();
+    if (item >= (long long)n * heads) {
+        pdl_wait();
+        return;
+    }
+    const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+    const int slot = (cache && h >= nh) ? slot_mapping[t] : 0;
+    pdl_wait();
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    const int d = (is_q || is_k) ? dk : dv;
+    T* src = qkv + (size_t)t * row_stride + (is_q || is_k ? (size_t)h * dk : (size_t)(nh + nkv) * dk + (size_t)(h - nh - nkv) * dv);
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+    const bool rope = (is_q || is_k) && cosr != nullptr;
+    float* s = sh[warp];
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        const float v = to_f32(src[i]);
+        s[i] = v;
+        ss += v * v;
+    }
+    float inv = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)d + eps);
+    }
+    __syncwarp();
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else if (cache) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        if (slot < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicExch(status, 2);
+            return;
+        }
+        const size_t page_elems = (size_t)nkv * page_size * (dk + dv);
+        dst = is_k ? cache + (size_t)page * page_elems + ((size_t)(h - nh) * page_size + off) * dk
+                   : cache + (size_t)page * page_elems + (size_t)nkv * page_size * dk + ((size_t)(h - nh - nkv) * page_size + off) * dv;
+    }
+    if (!dst) return;
+    const int half = rot >> 1;
+    for (int i = lane; i < d; i += 32) {
+        float v = w ? s[i] * inv * w[i] : s[i];
+        if (rope && i < rot) {
+            int j, pi;
+            bool first;
+            if (interleaved) {
+                j = i >> 1; first = (i & 1) == 0; pi = i ^ 1;
+            } else {
+                first = i < half; j = first ? i : i - half; pi = first ? i + half : i - half;
+            }
+            const float pv = w ? s[pi] * inv * w[pi] : s[pi];
+            const float c = cosr[(size_t)t * half + j], sn = sinr[(size_t)t * half + j];
+            v = first ? v * c - pv * sn : v * c + pv * sn;
+        }
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+VAPI_EXPORT int vapi_qk_norm_rope_write_split(void* qkv, long long row_stride, int dtype, const float* qw, const float* kw,
+                                              float eps, const float* cosr, const float* sinr, int rot, int interleaved,
+                                              void* cache, const int* slot_mapping, int n, int nh, int nkv, int dk,
+                                              int dv, int page_size, int num_pages, int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (dk <= 0 || dk > QK_MAX_D || dv <= 0 || dv > QK_MAX_D)
+        return fail(-1, "qk_norm_rope_write_split: head sizes %d/%d are outside 1..%d", dk, dv, QK_MAX_D);
+    if (cosr && (rot <= 0 || rot > dk || (rot % 2) != 0))
+        return fail(-1, "qk_norm_rope_write_split: rotary width %d does not fit head size %d", rot, dk);
+    if (nh <= 0 || nkv < 0) return fail(-1, "qk_norm_rope_write_split: bad head counts %d/%d", nh, nkv);
+    if (row_stride < (long long)(nh + nkv) * dk + (long long)nkv * dv)
+        return fail(-1, "qk_norm_rope_write_split: a row of %lld elements cannot hold the heads", row_stride);
+    if (cache && (page_size <= 0 || num_pages <= 0 || !slot_mapping))
+        return fail(-1, "qk_norm_rope_write_split: cache given without pages or slot mapping");
+    const long long items = (long long)n * (nh + 2 * nkv);
+    const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(qk_norm_rope_write_split_kernel<float>, blocks, QK_WARPS * 32, 0, stream, (float*)qkv, row_stride, qw, kw, eps,
+                   cosr, sinr, rot, interleaved, (float*)cache, slot_mapping, n, nh, nkv, dk, dv, page_size, num_pages, status);
+    else if (dtype == VAPI_BF16)
+        e = launch(qk_norm_rope_write_split_kernel<__nv_bfloat16>, blocks, QK_WARPS * 32, 0, stream, (__nv_bfloat16*)qkv,
+                   row_stride, qw, kw, eps, cosr, sinr, rot, interleaved, (__nv_bfloat16*)cache, slot_mapping, n, nh, nkv,
+                   dk, dv, page_size, num_pages, status);
+    else
+        return fail(-2, "qk_norm_rope_write_split: unsupported dtype %d", dtype);
+    return check_launch("qk_norm_rope_write_split", e);
+}
+
 VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

@@ -56,6 +56,8 @@ class ModelRunner:
         plan.bind(tensors, self.dtype)
         self.vocab_size = plan.vocab_size
         self.max_context = min(int(max_context or plan.max_positions), plan.max_positions)
+        if num_pages is not None:            # no request can hold more tokens than the pool has
+            self.max_context = min(self.max_context, int(num_pages) * int(page_size))
         self.max_batched_tokens = int(max_batched_tokens)
         # checking every batch on the host is a debugging aid (the reference does it in debug
         # builds, crates/vapi-backend-candle/src/backend.rs:486-487); VAPI_VALIDATE=1 forces it
@@ -83,6 +85,9 @@ class ModelRunner:
             owner = call.cache_of if call.cache_of is not None else i
             self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
         self._site_buffers = {s: self.cache.site_buffers(s) for s in set(self._site_of) if s is not None}
+        #: whether every block has the stream form that steps of few rows run (blocks without it hand
+        #: their output on in another shape than a plain delta, so such a model takes the ordinary path)
+        self._stream_form = all(hasattr(b, "forward_stream") for b in plan.layers)
         self.steps_run = 0
         self.graph_max_batch = min(64, max_requests)
         self._graphs: Dict[int, Any] = {}
@@ -170,7 +175,7 @@ class ModelRunner:
         for pe in plan.position_encodings:
             ctx.pos[pe.name] = pe.prepare(ctx)
         views = self.views(ctx)
-        ctx.fused = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and ops.use_skinny
+        ctx.fused = (self._stream_form and self.device.type == "cuda" and self.dtype == torch.bfloat16 and ops.use_skinny
                      and (ctx.n <= (ops.TC_MAX_ROWS if ops.use_tc else ops.SKINNY_MAX_ROWS)
                           or 0 < ops.PROMPT_MIN_ROWS <= ctx.n))
         if ctx.fused:

@@ -1010,3 +1010,267 @@ def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, toks: torch.Tensor
     _check(lib, lib.vapi_apply_penalties(_p(logits), logits.shape[1], ctypes.c_longlong(logits.stride(0)),
                                          _p(rows), _p(toks), _p(counts), _p(rep), _p(freq), _p(pres),
                                          rows.numel(), _stream()))
+
+
+# ---------------------------------------------------------------------------------------
+# blocks that norm a sublayer on both sides; rotary tables with scaled frequencies; attention
+# with unlike key and value widths, chunked masks, sinks and head gates; recurrent mixers
+def postnorm_add_rmsnorm(x: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float, mult: float,
+                         weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                         rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``x += mult * rmsnorm(y) * post_weight`` on the float32 stream and, with ``weight``,
+    ``out = rmsnorm(x) * weight`` in one pass.  With ``rows`` only those rows are produced and
+    ``x`` is left untouched.  ``weight`` None: only the stream is updated (returns None)."""
+    _cuda(x, y, post_weight, weight, rows)
+    _f32(x, "residual stream")
+    _f32(post_weight, "norm weight")
+    _f32(weight, "norm weight")
+    _i32(rows, "rows")
+    _contig(y, "sublayer output")
+    hidden = x.shape[-1]
+    if y.shape != x.shape or y.dtype != out_dtype:
+        raise KernelError("the sublayer's output must have the stream's shape and the activation dtype")
+    if post_weight.numel() != hidden or (weight is not None and weight.numel() != hidden):
+        raise KernelError(f"norm weights must have {hidden} elements")
+    n_out = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if weight is not None else None
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_postnorm_add_rmsnorm(_p(x), _p(y), _dt(y), _p(post_weight), ctypes.c_float(post_eps),
+                                              ctypes.c_float(mult), _p(weight), ctypes.c_float(eps), _p(rows), _p(out),
+                                              n_out, hidden, _stream()))
+    return out
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
+                        gate_first: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm over equal groups of ``group`` columns of the float32 rows ``y`` [n, width] with a
+    SiLU gate ``z`` [n, width] (any row stride): ``norm(y) * weight * silu(z)``, or with
+    ``gate_first`` ``norm(y * silu(z)) * weight``.  ``weight`` is indexed by column modulo its
+    length (one weight per group member, or one per column)."""
+    _cuda(y, z, weight)
+    _f32(y, "recurrence output")
+    _f32(weight, "norm weight")
+    n, width = y.shape
+    if z.shape != y.shape or z.stride(1) != 1 or z.dtype != out_dtype:
+        raise KernelError("the gate must be [n, width] of the activation dtype with unit inner stride")
+    out = torch.empty((n, width), dtype=out_dtype, device=y.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_gated_group_rmsnorm(_p(y), _p(z), ctypes.c_longlong(z.stride(0)), _dt(z), _p(weight),
+                                             weight.numel(), ctypes.c_float(eps), 1 if gate_first else 0, _p(out), n, width,
+                                             int(group), _stream()))
+    return out
+
+
+def scale_rows(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """``x *= factor`` in place on a contiguous float32 tensor."""
+    _cuda(x)
+    _f32(x, "rows")
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_scale(_p(x), ctypes.c_float(factor), ctypes.c_longlong(x.numel()), _stream()))
+    return x
+
+
+def rope_cos_sin_scaled(positions: torch.Tensor, freq: torch.Tensor, mult: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``mult * cos`` and ``mult * sin`` of ``position * freq`` in float32: two [n, len(freq)] tensors
+    (frequencies that an interpolation rule has already changed, and its multiplier)."""
+    _cuda(positions, freq)
+    _i32(positions, "positions")
+    _f32(freq, "frequencies")
+    n, half = positions.numel(), freq.numel()
+    cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    lib = _lib("rope")
+    _check(lib, lib.vapi_rope_cos_sin_scaled(_p(positions), _p(freq), ctypes.c_float(mult), _p(cos), _p(sin), n, half,
+                                             _stream()))
+    return cos, sin
+
+
+def qk_norm_rope_write_split(qkv: torch.Tensor, nh: int, nkv: int, dk: int, dv: int,
+                             q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                             cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, interleaved: bool,
+                             cache_layer: Optional[torch.Tensor], page_size: int, slot_mapping: Optional[torch.Tensor],
+                             status: Optional[torch.Tensor] = None) -> None:
+    """:func:`qk_norm_rope_write` for keys of width ``dk`` and values of width ``dv``: ``qkv`` [n, >=
+    (nh+nkv)*dk + nkv*dv] holds q heads, k heads, v heads (columns beyond them are left alone);
+    the rotation pairs (2i, 2i+1) when ``interleaved``, else (i, i + rot/2); ``cache_layer`` is the
+    call site's pages, flat [pages, page_size * nkv * (dk + dv)]: keys [nkv, page_size, dk], then
+    values [nkv, page_size, dv]."""
+    _cuda(qkv, q_weight, k_weight, cos, sin, cache_layer, slot_mapping)
+    _contig(qkv, "qkv")
+    _f32(q_weight, "q norm weight")
+    _f32(k_weight, "k norm weight")
+    _f32(cos, "cos")
+    _f32(sin, "sin")
+    _i32(slot_mapping, "slot mapping")
+    n = qkv.shape[0]
+    num_pages = 0
+    if cache_layer is not None:
+        _contig(cache_layer, "cache layer")
+        if cache_layer.dtype != qkv.dtype or cache_layer.dim() != 2 or cache_layer.shape[1] != page_size * nkv * (dk + dv):
+            raise KernelError(f"cache layer {tuple(cache_layer.shape)} / {cache_layer.dtype} does not fit pages of "
+                              f"{page_size} x {nkv} x ({dk} + {dv}) {qkv.dtype}")
+        num_pages = cache_layer.shape[0]
+    if cos is not None and (cos.shape != (n, rot // 2) or sin is None or sin.shape != cos.shape):
+        raise KernelError("cos/sin must be [n, rot/2]")
+    lib = _lib("rope")
+    _check(lib, lib.vapi_qk_norm_rope_write_split(
+        _p(qkv), ctypes.c_longlong(qkv.stride(0)), _dt(qkv), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(cos),
+        _p(sin), int(rot), 1 if interleaved else 0, _p(cache_layer), _p(slot_mapping), n, nh, nkv, dk, dv, int(page_size),
+        num_pages, _p(status), _stream()))
+
+
+def masked_attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
+    """How many blocks share the keys of one row tile of :func:`masked_attention`: 1 unless the step
+    leaves the device idle (few sequences decoding over long contexts)."""
+    rows = max_q * (nh // nkv)
+    blocks = max(1, num_seqs * nkv * -(-rows // 16))
+    sms = sm_count()
+    if blocks >= 2 * sms:
+        return 1
+    return max(1, min(4 * sms // blocks, max_k // 128, 32))
+
+
+def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tensor, page_size: int,
+                     block_table: torch.Tensor, cu_q: torch.Tensor, seqlens_k: torch.Tensor, n: int, num_seqs: int,
+                     max_q: int, max_k: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *, window: int = 0,
+                     chunk: int = 0, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                     splits: Optional[int] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal GQA attention of a mixed batch over the paged cache for keys of width ``dk`` and values
+    of width ``dv``; returns [n, nh*dv].  A query at position p sees key i iff i <= p, i > p - window
+    (``window`` > 0) and i // chunk == p // chunk (``chunk`` > 0).  ``sinks`` [nh] float32 adds
+    exp(sink_h) to head h's softmax denominator; ``gate`` [n, nh] (any row stride) multiplies head
+    h's output by sigmoid(gate).  ``cache_layer``: flat pages as for :func:`qk_norm_rope_write_split`."""
+    _cuda(q, cache_layer, block_table, cu_q, seqlens_k, sinks, gate)
+    _i32(block_table, "block table")
+    _i32(cu_q, "cu_q")
+    _i32(seqlens_k, "seqlens_k")
+    _f32(sinks, "sinks")
+    _contig(cache_layer, "cache layer")
+    if cache_layer.dtype != q.dtype:
+        raise KernelError("q and the cache must have one dtype")
+    if cache_layer.dim() != 2 or cache_layer.shape[1] != page_size * nkv * (dk + dv):
+        raise KernelError(f"cache layer {tuple(cache_layer.shape)} does not fit pages of {page_size} x {nkv} x ({dk} + {dv})")
+    if block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("block table must be [S, width] with unit inner stride")
+    if sinks is not None and sinks.numel() != nh:
+        raise KernelError("one sink per head is needed")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.shape != (n, nh) or gate.stride(1) != 1:
+            raise KernelError("the gate must be [n, heads] of the activation dtype with unit inner stride")
+        gate_stride = gate.stride(0)
+    if splits is None:
+        keys = max_k
+        if window > 0:
+            keys = min(keys, window + max_q - 1)
+        if chunk > 0:
+            keys = min(keys, chunk + max_q - 1)
+        splits = masked_attention_splits(num_seqs, max_q, keys, nh, nkv)
+    out = torch.empty((n, nh * dv), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n * nh * splits * dv,), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n * nh * splits * 2,), dtype=torch.float32, device=q.device)
+    lib = _lib("attention_masked")
+    _check(lib, lib.vapi_masked_attention(
+        _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table), block_table.stride(0), _p(cu_q),
+        _p(seqlens_k), _p(sinks), _p(gate), ctypes.c_longlong(gate_stride), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
+        max_q, nh, nkv, dk, dv, int(page_size), cache_layer.shape[0], ctypes.c_float(scale), int(window), int(chunk),
+        int(splits), _p(status), _stream()), 2 if splits > 1 else 1)
+    return out
+
+
+def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                     state_slots: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
+                     max_q: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(bias + causal depthwise convolution)`` of ``x`` [n, C] (a column range of a wider tensor
+    is fine: unit inner stride, any row stride) with ``taps`` [L, C] float32, oldest first.  ``state``
+    [slots, >= (L-1)*C] float32 holds each request's last L-1 inputs at its front and is moved on.
+    Returns [n, C] in x's dtype."""
+    _cuda(x, taps, bias, state, state_slots, tok_seq, cu_q, positions)
+    _f32(taps, "conv taps")
+    _f32(bias, "conv bias")
+    for t, w in ((state_slots, "state slots"), (tok_seq, "tok_seq"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    n, C = x.shape
+    L = taps.shape[0]
+    if x.stride(1) != 1 or taps.shape[1] != C:
+        raise KernelError("x must be [n, C] with unit inner stride and taps [L, C]")
+    slot_stride = num_slots = 0
+    if L > 1:
+        if state is None or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < (L - 1) * C:
+            raise KernelError(f"the state must be float32 [slots, >= {(L - 1) * C}] with unit inner stride")
+        slot_stride, num_slots = state.stride(0), state.shape[0]
+    out = torch.empty((n, C), dtype=x.dtype, device=x.device)
+    lib = _lib("recurrent")
+    _check(lib, lib.vapi_causal_conv_silu(
+        _p(x), ctypes.c_longlong(x.stride(0)), _dt(x), _p(taps), _p(bias), _p(state if L > 1 else None),
+        ctypes.c_longlong(slot_stride), _p(state_slots), _p(tok_seq), _p(cu_q), _p(positions), _p(out), n,
+        cu_q.numel() - 1, C, L, num_slots, int(max_q), _p(status), _stream()))
+    return out
+
+
+def gated_delta(qkv: torch.Tensor, ab: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+                state_offset: int, state_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor, nh: int,
+                nkv: int, dk: int, dv: int, norm_eps: float = 1e-6, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The gated delta rule over every sequence of the step.  ``qkv`` [n, 2*nkv*dk + nh*dv] holds q
+    heads, k heads (``nkv`` of ``dk``) and v heads (``nh`` of ``dv``); ``ab`` [n, 2*nh] (unit inner
+    stride, any row stride) holds the decay's pre-activation a and the write strength's
+    pre-activation b.  Per head: q, k made unit vectors (``norm_eps`` inside the root; q also times
+    dk^-1/2); ``S <- g S; u = sigmoid(b) (v - S^T k); S <- S + k u^T; o = S^T q`` with
+    ``g = exp(-exp(A_log) softplus(a + dt_bias))``.  ``state`` [slots, >= state_offset + nh*dk*dv]
+    float32 carries S [nh, dk, dv] at ``state_offset``.  Returns o [n, nh*dv] float32."""
+    _cuda(qkv, ab, A_log, dt_bias, state, state_slots, cu_q, positions)
+    _contig(qkv, "qkv")
+    _f32(A_log, "A_log")
+    _f32(dt_bias, "dt_bias")
+    for t, w in ((state_slots, "state slots"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    n = qkv.shape[0]
+    if qkv.shape[1] != 2 * nkv * dk + nh * dv:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {2 * nkv * dk + nh * dv}")
+    if ab.dtype != qkv.dtype or ab.shape != (n, 2 * nh) or ab.stride(1) != 1:
+        raise KernelError("a|b must be [n, 2*heads] of qkv's dtype with unit inner stride")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < state_offset + nh * dk * dv:
+        raise KernelError("the state must be float32 [slots, >= offset + heads*dk*dv] with unit inner stride")
+    out = torch.empty((n, nh * dv), dtype=torch.float32, device=qkv.device)
+    lib = _lib("recurrent")
+    _check(lib, lib.vapi_gated_delta(
+        _p(qkv), ctypes.c_longlong(qkv.stride(0)), 0, nkv * dk, 2 * nkv * dk, _p(ab), ctypes.c_longlong(ab.stride(0)),
+        _dt(qkv), _p(A_log), _p(dt_bias), ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)),
+        ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, nkv,
+        dk, dv, state.shape[0], ctypes.c_float(norm_eps), _p(status), _stream()))
+    return out
+
+
+def state_space(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
+                state: torch.Tensor, state_offset: int, state_slots: torch.Tensor, cu_q: torch.Tensor,
+                positions: torch.Tensor, nh: int, groups: int, n_state: int, head: int,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The selective state-space recurrence of Mamba-2 over every sequence of the step.  ``xbc``
+    [n, nh*head + 2*groups*n_state] holds x heads, then B and C per group; ``dt`` [n, nh] (unit inner
+    stride, any row stride) the step sizes' pre-activations.  Per head, with
+    ``step = softplus(dt + dt_bias)``: ``S <- exp(-exp(A_log) step) S + step B x^T; y = S^T C + D x``.
+    ``state`` carries S [nh, n_state, head] float32 at ``state_offset``.  Returns y [n, nh*head] float32."""
+    _cuda(xbc, dt, A_log, dt_bias, D, state, state_slots, cu_q, positions)
+    _contig(xbc, "x|B|C")
+    _f32(A_log, "A_log")
+    _f32(dt_bias, "dt_bias")
+    _f32(D, "D")
+    for t, w in ((state_slots, "state slots"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    n = xbc.shape[0]
+    if xbc.shape[1] != nh * head + 2 * groups * n_state:
+        raise KernelError(f"x|B|C has {xbc.shape[1]} columns, expected {nh * head + 2 * groups * n_state}")
+    if dt.dtype != xbc.dtype or dt.shape != (n, nh) or dt.stride(1) != 1:
+        raise KernelError("dt must be [n, heads] of x's dtype with unit inner stride")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < state_offset + nh * n_state * head:
+        raise KernelError("the state must be float32 [slots, >= offset + heads*state*head] with unit inner stride")
+    out = torch.empty((n, nh * head), dtype=torch.float32, device=xbc.device)
+    lib = _lib("recurrent")
+    _check(lib, lib.vapi_state_space(
+        _p(xbc), ctypes.c_longlong(xbc.stride(0)), _p(dt), ctypes.c_longlong(dt.stride(0)), _dt(xbc), _p(A_log),
+        _p(dt_bias), _p(D), ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)), ctypes.c_longlong(state.stride(0)),
+        _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, groups, n_state, head, state.shape[0],
+        _p(status), _stream()))
+    return out

@@ -7,7 +7,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import CacheView, Mixer, PagedSpec, StreamState, TensorSpec, register_mixer
+from .base import CacheView, Mixer, PagedBuffer, PagedSpec, StreamState, TensorSpec, register_mixer
 
 
 class GQAttention(Mixer):
@@ -20,16 +20,38 @@ class GQAttention(Mixer):
     ``q k v o q_norm k_norm`` to checkpoint sub-names, so another architecture's naming is a
     parameter, not a subclass.  ``pos`` names the position encoding whose ``(cos, sin)`` to
     apply (None: no rotation).
+
+    Options beyond the plain form, each a parameter: ``v_head_dim`` (values of another width than
+    queries and keys), ``chunk`` (a query sees only keys of its own block of ``chunk`` positions,
+    counted from position 0), ``sink`` (a learned number per head whose exponential joins the
+    softmax's denominator), ``head_gate`` (head h's output times ``sigmoid(W_g x)_h``, the gate's
+    rows riding on the fused projection), ``rope_layout`` ("half": pairs (i, i + rot/2);
+    "interleaved": pairs (2i, 2i+1)) and ``weight_suffix`` (what follows a projection's name in the
+    checkpoint).  Any of the first five sends the mixer to the general kernels
+    (``ops.qk_norm_rope_write_split``, ``ops.masked_attention``); the plain form keeps the
+    specialised ones.
     """
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, *,
                  qk_norm_eps: Optional[float] = None, pos: Optional[str] = "rope",
                  rot_dim: Optional[int] = None, window: int = 0, bias: bool = False,
-                 scale: Optional[float] = None, names: Optional[Dict[str, str]] = None):
+                 scale: Optional[float] = None, names: Optional[Dict[str, str]] = None,
+                 v_head_dim: Optional[int] = None, chunk: int = 0, sink: bool = False, head_gate: bool = False,
+                 rope_layout: str = "half", weight_suffix: str = ".weight"):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-        if head_dim % 16 or not 16 <= head_dim <= 256:
+        if rope_layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary layout `{rope_layout}` is not one of half, interleaved")
+        self.dv = int(v_head_dim) if v_head_dim is not None else int(head_dim)
+        self.chunk, self.sink, self.head_gate = int(chunk), bool(sink), bool(head_gate)
+        self.interleaved = rope_layout == "interleaved"
+        self.general = bool(self.dv != int(head_dim) or self.chunk > 0 or self.sink or self.head_gate or self.interleaved)
+        if self.general:
+            if head_dim % 4 or self.dv % 4 or not (4 <= head_dim <= 256 and 4 <= self.dv <= 256):
+                raise ValueError(f"head sizes {head_dim} / {self.dv} must be multiples of 4 in 4..256")
+        elif head_dim % 16 or not 16 <= head_dim <= 256:
             raise ValueError(f"head_dim {head_dim} must be a multiple of 16 in 16..256")
+        self.sfx = weight_suffix
         self.hidden, self.nh, self.nkv, self.d = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
         self.qk_norm_eps = qk_norm_eps
         self.pos = pos
@@ -38,45 +60,65 @@ class GQAttention(Mixer):
         self.bias = bool(bias)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.d)
         self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "out_proj",
-                      "q_norm": "q_layernorm", "k_norm": "k_layernorm"}
+                      "q_norm": "q_layernorm", "k_norm": "k_layernorm", "sink": "sinks", "gate": "gate_proj"}
         if names:
             self.names.update(names)
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_w = self.k_w = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_w = self.k_w = self.sinks = None
 
     def cache_spec(self):
-        return PagedSpec.kv(self.nkv, self.d, self.window)
+        # (for equal widths this is PagedSpec.kv: keys [nkv, page, d], then values [nkv, page, dv])
+        return PagedSpec((PagedBuffer("k", self.nkv, self.d), PagedBuffer("v", self.nkv, self.dv)), self.window)
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
-        n, (h, nh, nkv, d) = self.names, (self.hidden, self.nh, self.nkv, self.d)
-        specs = [TensorSpec(f"{prefix}{n['q']}.weight", (nh * d, h)),
-                 TensorSpec(f"{prefix}{n['k']}.weight", (nkv * d, h)),
-                 TensorSpec(f"{prefix}{n['v']}.weight", (nkv * d, h)),
-                 TensorSpec(f"{prefix}{n['o']}.weight", (h, nh * d))]
+        n, (h, nh, nkv, d), x = self.names, (self.hidden, self.nh, self.nkv, self.d), self.sfx
+        specs = [TensorSpec(f"{prefix}{n['q']}{x}", (nh * d, h)),
+                 TensorSpec(f"{prefix}{n['k']}{x}", (nkv * d, h)),
+                 TensorSpec(f"{prefix}{n['v']}{x}", (nkv * self.dv, h)),
+                 TensorSpec(f"{prefix}{n['o']}{x}", (h, nh * self.dv))]
+        if self.head_gate:
+            specs.append(TensorSpec(f"{prefix}{n['gate']}{x}", (nh, h)))
+        if self.sink:
+            specs.append(TensorSpec(f"{prefix}{n['sink']}", (nh,), role="vector", init="normal"))
         if self.bias:
             specs += [TensorSpec(f"{prefix}{n['q']}.bias", (nh * d,), role="vector"),
                       TensorSpec(f"{prefix}{n['k']}.bias", (nkv * d,), role="vector"),
-                      TensorSpec(f"{prefix}{n['v']}.bias", (nkv * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['v']}.bias", (nkv * self.dv,), role="vector"),
                       TensorSpec(f"{prefix}{n['o']}.bias", (h,), role="vector")]
         if self.qk_norm_eps is not None:
-            specs += [TensorSpec(f"{prefix}{n['q_norm']}.weight", (d,), role="vector", init="ones"),
-                      TensorSpec(f"{prefix}{n['k_norm']}.weight", (d,), role="vector", init="ones")]
+            specs += [TensorSpec(f"{prefix}{n['q_norm']}{x}", (d,), role="vector", init="ones"),
+                      TensorSpec(f"{prefix}{n['k_norm']}{x}", (d,), role="vector", init="ones")]
         return specs
 
     def bind(self, tensors, prefix, dtype):
-        n = self.names
-        parts = [tensors[f"{prefix}{n[r]}.weight"] for r in ("q", "k", "v")]
+        n, x = self.names, self.sfx
+        parts = [tensors[f"{prefix}{n[r]}{x}"] for r in ("q", "k", "v")]
+        if self.head_gate:
+            parts.append(tensors[f"{prefix}{n['gate']}{x}"])
         wd = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
+        if self.general:
+            # rows of the fused product stay 16-byte aligned whatever the gate adds
+            rows = sum(p.shape[0] for p in parts)
+            if rows % 8:
+                parts.append(torch.zeros((8 - rows % 8, self.hidden), dtype=wd, device=parts[0].device))
         self.w_qkv = torch.cat([p.to(wd) for p in parts], 0).contiguous()
-        self.w_o = tensors[f"{prefix}{n['o']}.weight"].contiguous()
+        self.w_o = tensors[f"{prefix}{n['o']}{x}"].contiguous()
+        if self.sink:
+            self.sinks = tensors[f"{prefix}{n['sink']}"].contiguous()
         if self.bias:
             self.b_qkv = torch.cat([tensors[f"{prefix}{n[r]}.bias"] for r in ("q", "k", "v")], 0).contiguous()
+            if self.b_qkv.numel() < self.w_qkv.shape[0]:       # the gate's rows and the padding have no bias
+                self.b_qkv = torch.cat([self.b_qkv, self.b_qkv.new_zeros(self.w_qkv.shape[0] - self.b_qkv.numel())])
             self.b_o = tensors[f"{prefix}{n['o']}.bias"].contiguous()
         if self.qk_norm_eps is not None:
-            self.q_w = tensors[f"{prefix}{n['q_norm']}.weight"].contiguous()
-            self.k_w = tensors[f"{prefix}{n['k_norm']}.weight"].contiguous()
+            self.q_w = tensors[f"{prefix}{n['q_norm']}{x}"].contiguous()
+            self.k_w = tensors[f"{prefix}{n['k_norm']}{x}"].contiguous()
 
     def decode_splits(self, batch: int, max_context: int, page_size: int, dtype: torch.dtype) -> int:
         keys = min(max_context, self.window) if self.window > 0 else max_context
+        if self.general:
+            if self.chunk > 0:
+                keys = min(keys, self.chunk)
+            return ops.masked_attention_splits(batch, 1, keys, self.nh, self.nkv)
         dec = ops.decode_attention_applies(dtype, self.d, page_size, self.nh // self.nkv)
         return ops.attention_splits(batch, 1, keys, self.nh, self.nkv, dec)
 
@@ -99,6 +141,8 @@ class GQAttention(Mixer):
         if self.pos is not None:
             cos, sin = ctx.pos[self.pos]
         grp = cache.group
+        if self.general:
+            return self._attend_general(qkv, ctx, cache, cos, sin)
         n_rep = nh // nkv
         kv = cache.stacked() if cache.tensor is not None else None      # [pages, 2, n_kv, page_size, head_dim]
         splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
@@ -123,6 +167,28 @@ class GQAttention(Mixer):
                                 ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d,
                                 self.scale, self.window, splits, ctx.status)
         return y
+
+
+    def _attend_general(self, qkv, ctx, cache, cos, sin):
+        """Unlike key and value widths, a chunked mask, a sink, a head gate or interleaved pairs."""
+        nh, nkv, d, dv = self.nh, self.nkv, self.d, self.dv
+        grp = cache.group
+        pages = cache.tensor                                    # flat [pages, page_size * nkv * (d + dv)]
+        page_size = pages.shape[1] // (nkv * (d + dv))
+        ops.qk_norm_rope_write_split(qkv, nh, nkv, d, dv, self.q_w, self.k_w,
+                                     self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, self.rot_dim,
+                                     self.interleaved, pages if cache.write else None, page_size, grp.slot_mapping,
+                                     ctx.status)
+        gate = None
+        if self.head_gate:
+            off = (nh + nkv) * d + nkv * dv
+            gate = qkv[:, off:off + nh]
+        splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
+        max_k = getattr(grp, "max_k", None) or ctx.max_k
+        return ops.masked_attention(qkv, qkv.stride(0), pages, page_size, grp.block_table, ctx.cu_q, ctx.seqlens_k,
+                                    ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d, dv, self.scale,
+                                    window=self.window, chunk=self.chunk, sinks=self.sinks, gate=gate, splits=splits,
+                                    status=ctx.status)
 
 
 register_mixer("gqa_attention", GQAttention)

@@ -166,6 +166,19 @@ class NormedStream:
     eps: float
 
 
+@dataclass
+class PostNormed:
+    """A sublayer's output that is still to be normed, scaled and added into the residual stream:
+    ``x <- x + mult * rmsnorm(y) * weight``.  Blocks that norm a sublayer on both sides hand this
+    on instead of a plain delta, and the norm that reads the stream next does the whole update
+    while it reads the row (:meth:`Norm.apply` accepts it wherever it accepts a delta)."""
+
+    y: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    mult: float = 1.0
+
+
 # --------------------------------------------------------------------------------------
 # the parts
 
@@ -186,7 +199,7 @@ class Norm(Part):
     def apply(self, x: torch.Tensor, delta: Optional[torch.Tensor], dtype: torch.dtype,
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x`` is the float32 residual stream [n, H].  Adds ``delta`` (a layer's output in
-        the activation dtype) into it when given, and returns the normed rows in ``dtype``.
+        the activation dtype, or a :class:`PostNormed`) into it when given, and returns the normed rows in ``dtype``.
         With ``rows`` only those rows are produced and ``x`` is left unchanged."""
         raise NotImplementedError
 

@@ -5,7 +5,7 @@ from typing import Any, Callable, Dict, List, Optional
 
 import torch
 
-from .base import CacheView, FeedForward, Mixer, Norm, Part, StreamState, TensorSpec
+from .base import CacheView, FeedForward, Mixer, Norm, Part, PostNormed, StreamState, TensorSpec
 
 BLOCKS: Dict[str, Callable[..., "Part"]] = {}
 
@@ -88,4 +88,56 @@ class PreNormBlock(Part):
         return StreamState(xw, ss)
 
 
+class SandwichBlock(Part):
+    """A norm before and after each sublayer, and a multiplier on what the sublayer adds:
+
+        x <- x + mult * post_m(mixer(pre_m(x)));   x <- x + mult * post_f(ffn(pre_f(x)))
+
+    ``ffn`` may be None: the block then has only the first sublayer.  A sublayer's output is not
+    normed and added by a kernel of its own: it is handed on as a :class:`PostNormed`, and the norm
+    that reads the stream next (this block's second pre-norm, the next block's first, or the
+    model's final norm) norms, scales and adds it while it reads the row.
+
+    ``sub`` gives the checkpoint sub-prefix of each part (``mixer_norm``, ``mixer_post``, ``mixer``,
+    ``ffn_norm``, ``ffn_post``, ``ffn``).  The post-norms must be RMS norms (their weight and eps are
+    what is handed on).
+    """
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, mixer_post: Norm, ffn_norm: Optional[Norm],
+                 ffn: Optional[FeedForward], ffn_post: Optional[Norm], sub: Dict[str, str], mult: float = 1.0):
+        if (ffn is None) != (ffn_norm is None) or (ffn is None) != (ffn_post is None):
+            raise ValueError("a feed-forward comes with both of its norms or not at all")
+        self.mixer_norm, self.mixer, self.mixer_post = mixer_norm, mixer, mixer_post
+        self.ffn_norm, self.ffn, self.ffn_post = ffn_norm, ffn, ffn_post
+        self.sub, self.mult = dict(sub), float(mult)
+
+    def _parts(self):
+        out = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer), ("mixer_post", self.mixer_post)]
+        if self.ffn is not None:
+            out += [("ffn_norm", self.ffn_norm), ("ffn", self.ffn), ("ffn_post", self.ffn_post)]
+        return out
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        out: List[TensorSpec] = []
+        for key, part in self._parts():
+            out += part.tensor_specs(prefix + self.sub.get(key, ""))
+        return out
+
+    def bind(self, tensors, prefix, dtype):
+        for key, part in self._parts():
+            part.bind(tensors, prefix + self.sub.get(key, ""), dtype)
+
+    def first_norm(self) -> Norm:
+        return self.mixer_norm
+
+    def forward(self, x: torch.Tensor, delta, ctx: Any, cache: CacheView) -> PostNormed:
+        a = self.mixer_norm.apply(x, delta, ctx.dtype)
+        pending = PostNormed(self.mixer.forward(a, ctx, cache), self.mixer_post.weight, self.mixer_post.eps, self.mult)
+        if self.ffn is None:
+            return pending
+        f = self.ffn_norm.apply(x, pending, ctx.dtype)
+        return PostNormed(self.ffn.forward(f, ctx), self.ffn_post.weight, self.ffn_post.eps, self.mult)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

@@ -35,8 +35,10 @@ class OutputHead(Part):
     (crates/vapi-backend-candle/src/models/lfm2.rs:676-680, 803-818)."""
 
     def __init__(self, vocab: int, hidden: int, tied: bool, embedding: TokenEmbedding,
-                 name: str = "lm_head.weight"):
+                 name: str = "lm_head.weight", scale: float = 1.0):
         self.vocab, self.hidden, self.tied, self.embedding, self.name = int(vocab), int(hidden), bool(tied), embedding, name
+        #: the logits are multiplied by this number (in float32, after the product)
+        self.scale = float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self, prefix: str = "") -> List[TensorSpec]:
@@ -50,10 +52,12 @@ class OutputHead(Part):
         self.weight = (w if w is not None else tensors[self.embedding.name]).contiguous()
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
-        return ops.linear(xn, self.weight, None, torch.float32)
+        logits = ops.linear(xn, self.weight, None, torch.float32)
+        return logits if self.scale == 1.0 else ops.scale_rows(logits, self.scale)
 
     def forward_stream(self, a):
         """Logits of every row of a lazily normed stream (decode steps), or NotImplemented."""
         if not ops.few_rows_applies(a.xw.shape[0], self.weight):
             return NotImplemented
-        return ops.few_rows_linear(self.weight, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="f32")
+        logits = ops.few_rows_linear(self.weight, xw=a.xw, ss_in=a.ss, eps=a.eps, epilogue="f32")
+        return logits if self.scale == 1.0 else ops.scale_rows(logits, self.scale)

@@ -15,8 +15,8 @@ class SwiGLU(FeedForward):
     (crates/vapi-backend-candle/src/models/lfm2.rs:568-595).  ``names`` maps gate/up/down to
     the checkpoint's sub-names (LFM2: w1 / w3 / w2)."""
 
-    def __init__(self, hidden: int, ff: int, names: Optional[Dict[str, str]] = None):
-        self.hidden, self.ff = int(hidden), int(ff)
+    def __init__(self, hidden: int, ff: int, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight"):
+        self.hidden, self.ff, self.sfx = int(hidden), int(ff), weight_suffix
         self.names = {"gate": "w1", "up": "w3", "down": "w2"}
         if names:
             self.names.update(names)
@@ -24,16 +24,16 @@ class SwiGLU(FeedForward):
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         n = self.names
-        return [TensorSpec(f"{prefix}{n['gate']}.weight", (self.ff, self.hidden)),
-                TensorSpec(f"{prefix}{n['up']}.weight", (self.ff, self.hidden)),
-                TensorSpec(f"{prefix}{n['down']}.weight", (self.hidden, self.ff))]
+        return [TensorSpec(f"{prefix}{n['gate']}{self.sfx}", (self.ff, self.hidden)),
+                TensorSpec(f"{prefix}{n['up']}{self.sfx}", (self.ff, self.hidden)),
+                TensorSpec(f"{prefix}{n['down']}{self.sfx}", (self.hidden, self.ff))]
 
     def bind(self, tensors, prefix, dtype):
         n = self.names
-        g, u = tensors[f"{prefix}{n['gate']}.weight"], tensors[f"{prefix}{n['up']}.weight"]
+        g, u = tensors[f"{prefix}{n['gate']}{self.sfx}"], tensors[f"{prefix}{n['up']}{self.sfx}"]
         wd = g.dtype if g.dtype == u.dtype else torch.float32
         self.w_gate_up = torch.cat([g.to(wd), u.to(wd)], 0).contiguous()
-        self.w_down = tensors[f"{prefix}{n['down']}.weight"].contiguous()
+        self.w_down = tensors[f"{prefix}{n['down']}{self.sfx}"].contiguous()
 
     def forward(self, f: torch.Tensor, ctx: Any) -> torch.Tensor:
         return ops.linear(ops.linear_swiglu(f, self.w_gate_up), self.w_down)

@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import Norm, NormedStream, TensorSpec, register_norm
+from .base import Norm, NormedStream, PostNormed, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
@@ -25,6 +25,9 @@ class RMSNorm(Norm):
         self.weight = tensors[f"{prefix}{self.weight_name}"].contiguous()
 
     def apply(self, x, delta, dtype, rows=None):
+        if isinstance(delta, PostNormed):
+            return ops.postnorm_add_rmsnorm(x, delta.y, delta.weight, delta.eps, delta.mult, self.weight, self.eps,
+                                            dtype, rows)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, dtype, rows)
 
     def stream_weight(self):
