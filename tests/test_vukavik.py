@@ -35,7 +35,7 @@ def _folder(tmp_path_factory, name, cfg, seed, dtype=torch.float32):
 def folders(tmp_path_factory):
     out = {}
     for name, cfg, seed in (("mixed", vu.MIXED, 1), ("tiny", vu.TINY, 2), ("no_attention", vu.NO_ATTENTION, 3),
-                            ("plain_attention", vu.PLAIN_ATTENTION, 4)):
+                            ("plain_attention", vu.PLAIN_ATTENTION, 4), ("serving_heads", vu.SERVING_HEADS, 6)):
         out[name] = _folder(tmp_path_factory, name, cfg, seed)
         out[name + "/bf16"] = vu.write_model(str(tmp_path_factory.mktemp(name + "bf16")), cfg, seed, torch.bfloat16, std=0.05)
     for kind, layer in (("attention", vu.attention(ff=None)), ("delta", vu.delta()), ("mamba2", vu.mamba2()),
@@ -53,12 +53,14 @@ def _check(runner, oracle, requests, schedule, dtype):
         err, pos = vu.worst(got[rid], oracle.logits(toks))
         if dtype == "bfloat16":
             # The norm behind every sublayer enlarges the rounding of a sublayer whose output happens to be
-            # small, so single positions stand out: measured on these models, 300 positions: mean 1.0 %,
-            # 95th percentile 1.9 %, worst 3.4 % of the logit range.
+            # small, so single positions stand out, the same ones whichever kernels run: measured on these
+            # models over 300 positions, mean 1.0 to 1.1 %, 95th percentile 1.9 to 2.8 %, worst 3.4 to 11 % of
+            # the logit range (the general attention kernel and the tensor-core ones within 1 % of each
+            # other at every position).  Edges are what the float32 cases and the planted keys pin down.
             want = oracle.logits(toks).numpy()
             e = np.abs(got[rid] - want).max(-1) / float(want.max() - want.min())
-            assert np.percentile(e, 95) <= vu.limit(dtype) and err <= 2 * vu.limit(dtype), \
-                f"request {rid}: 95th percentile {np.percentile(e, 95):.3e}, worst {err:.3e} of the logit range at {pos}"
+            assert e.mean() <= 0.02 and np.percentile(e, 95) <= vu.limit(dtype) and err <= 0.15, \
+                f"request {rid}: mean {e.mean():.3e}, 95th percentile {np.percentile(e, 95):.3e}, worst {err:.3e} of the logit range at {pos}"
         else:
             assert err <= vu.limit(dtype), f"request {rid}: {err:.3e} of the logit range at position {pos} of {len(toks)}"
 
@@ -185,11 +187,13 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(device, name, 
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["mixed", "plain_attention"])
-def test_bfloat16_serving_path(name, folders, kernels):
+@pytest.mark.parametrize("name,page", [("mixed", 16), ("plain_attention", 16), ("serving_heads", 64)])
+def test_bfloat16_serving_path(name, page, folders, kernels):
+    """(`serving_heads`: keys and values of 64 and of 128 on pages of 64 tokens, the shapes that the
+    tensor-core attention kernels take.)"""
     kernels("cuda")
     oracle = vu.Oracle(folders[name + "/bf16"])
-    runner = vu.make_runner(folders[name + "/bf16"], "bfloat16", "cuda", num_pages=24, max_tokens=512)
+    runner = vu.make_runner(folders[name + "/bf16"], "bfloat16", "cuda", num_pages=24, max_tokens=512, page_size=page)
     reqs = {"a": vu.prompt(oracle.cfg, 300, 41), "b": vu.prompt(oracle.cfg, 45, 42)}
     _check(runner, oracle, reqs, [[("a", 300)], [("b", 45)]], "bfloat16")
     _check(runner, oracle, reqs, [[("a", 270), ("b", 2)], [("a", 1), ("b", 20)]] + [[("a", 1), ("b", 1)]] * 23 + [[("a", 1)]] * 6,
@@ -217,17 +221,20 @@ def _planted(klen, qlen, j_star, dk=16, dv=8, page=16, nh=2, nkv=1, device="cuda
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("qlen", [1, 5, 40])
-def test_a_planted_key_is_seen_exactly_where_the_mask_allows(qlen, dtype):
+@pytest.mark.parametrize("dk,dv,page", [(16, 8, 16), (64, 64, 64), (128, 128, 64)])
+@pytest.mark.parametrize("qlen", [1, 5, 40, 100])
+def test_a_planted_key_is_seen_exactly_where_the_mask_allows(qlen, dk, dv, page, dtype):
+    """In bfloat16 the equal widths run on the tensor-core kernels (one warp for few rows, four warps,
+    tcgen05 from 64 tokens on), everything else on the general kernel."""
     from vapi_b200 import ops
-    chunk, klen = 48, 150                                     # chunks end inside pages of 16
+    chunk, klen = 48, 150                                     # chunks end inside pages
     for j_star in (3, 47, 48, 95, 96, 143, 144, 149):
-        q, cache, table = _planted(klen, qlen, j_star, dtype=dtype)
+        q, cache, table = _planted(klen, qlen, j_star, dk=dk, dv=dv, page=page, dtype=dtype)
         cu = torch.tensor([0, qlen], dtype=torch.int32, device="cuda")
         kl = torch.tensor([klen], dtype=torch.int32, device="cuda")
         sinks = torch.tensor([-30.0, -30.0], device="cuda")
         for ch, splits in ((chunk, 1), (chunk, 3), (0, 1), (0, 4)):
-            out = ops.masked_attention(q, q.stride(0), cache, 16, table, cu, kl, qlen, 1, qlen, klen, 2, 1, 16, 8, 1.0,
+            out = ops.masked_attention(q, q.stride(0), cache, page, table, cu, kl, qlen, 1, qlen, klen, 2, 1, dk, dv, 1.0,
                                        chunk=ch, sinks=sinks, splits=splits).float().cpu()
             for i in range(qlen):
                 p = klen - qlen + i
@@ -237,24 +244,27 @@ def test_a_planted_key_is_seen_exactly_where_the_mask_allows(qlen, dtype):
 
 
 @pytest.mark.gpu
-def test_a_far_key_among_hundreds_and_the_sink_and_the_gate():
+@pytest.mark.parametrize("dtype,dk,dv,page,qlen", [(torch.float32, 16, 8, 16, 1), (torch.bfloat16, 64, 64, 64, 1),
+                                                   (torch.bfloat16, 64, 64, 64, 70), (torch.bfloat16, 128, 128, 64, 20)])
+def test_a_far_key_among_hundreds_and_the_sink_and_the_gate(dtype, dk, dv, page, qlen):
     from vapi_b200 import ops
     klen = 900
-    q, cache, table = _planted(klen, 1, 2)
-    cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    q, cache, table = _planted(klen, qlen, 2, dk=dk, dv=dv, page=page, dtype=dtype)
+    cu = torch.tensor([0, qlen], dtype=torch.int32, device="cuda")
     kl = torch.tensor([klen], dtype=torch.int32, device="cuda")
-    args = (q, q.stride(0), cache, 16, table, cu, kl, 1, 1, 1, klen, 2, 1, 16, 8, 1.0)
+    args = (q, q.stride(0), cache, page, table, cu, kl, qlen, 1, qlen, klen, 2, 1, dk, dv, 1.0)
+    tol = 0.01 if dtype == torch.float32 else 0.03
     for splits in (1, 5):
         out = ops.masked_attention(*args, splits=splits)
-        assert abs(float(out.mean()) - 1.0) < 0.01
+        assert abs(float(out.float().mean()) - 1.0) < tol
         # a sink as strong as the planted key's score halves the weights; a zero gate halves them again
-        score = float((q[0, :16] * cache[int(table[0, 0]), 2 * 16:3 * 16]).sum())
+        score = float((q[-1, :dk].float() * cache[int(table[0, 0]), 2 * dk:3 * dk].float()).sum())
         sinks = torch.tensor([score, -1e4], device="cuda")
-        gate = torch.tensor([[0.0, 30.0]], device="cuda")
-        out = ops.masked_attention(*args, sinks=sinks, gate=gate, splits=splits).cpu()
-        assert abs(float(out[0, :8].mean()) - 0.25) < 0.01 and abs(float(out[0, 8:].mean()) - 1.0) < 0.01
+        gate = torch.tensor([[0.0, 30.0]] * qlen, device="cuda", dtype=dtype)
+        out = ops.masked_attention(*args, sinks=sinks, gate=gate, splits=splits).float().cpu()
+        assert abs(float(out[-1, :dv].mean()) - 0.25) < tol and abs(float(out[-1, dv:].mean()) - 1.0) < tol
     want = plain_ops.masked_attention(*[a.cpu() if torch.is_tensor(a) else a for a in args], sinks=sinks.cpu(), gate=gate.cpu())
-    assert torch.allclose(out, want, atol=1e-4)
+    assert torch.allclose(out, want.float(), atol=1e-4 if dtype == torch.float32 else 3e-2)
 
 
 # ---- the recurrent kernels against their restatements, at sizes that are not powers of two ----------------------

@@ -54,6 +54,11 @@ NO_ATTENTION = config([mamba2(ff=64), delta()], residual_mult=1.0, logit_scale=1
 PLAIN_ATTENTION = config([attention(chunk=None, scaling=None, rot_dims=8), attention(chunk=None, scaling=None, rot_dims=0, heads=2, kv_heads=1, dim=32, vdim=32)])
 
 
+#: keys and values of 64 and of 128, the widths of the tensor-core attention kernels; chunks that end inside pages of 64
+SERVING_HEADS = config([attention(heads=4, kv_heads=2, dim=64, vdim=64, chunk=100, rot_dims=32, ff=128), delta(heads=2, kv_heads=1, dim=32, vdim=32),
+                        attention(heads=2, kv_heads=1, dim=128, vdim=128, chunk=None, rot_dims=128, ff=None)], width=128)
+
+
 def write_model(folder: str, cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.12) -> str:
     """A model folder whose small parameters are far from their neutral values (decays, step
     biases, sinks, skips, taps, norm weights), so that leaving one out shows."""

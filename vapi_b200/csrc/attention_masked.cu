@@ -12,12 +12,20 @@
 //
 // A cache page holds the keys [nkv, page_size, dk] and then the values [nkv, page_size, dv].
 //
+// bfloat16 with keys and values of one width, 64 or 128, and pages of a multiple of 64 tokens runs on
+// the tensor cores: the flash kernel of attention_mma.cuh (four warps for prompt portions, one warp
+// per 16 rows and split keys for decode steps) and, for prompt portions of 64 tokens and more at
+// width 64, the tcgen05 kernel of attention_tc.cuh; both take the mask, the sink and the gate as
+// parameters.  Everything else (float32, unlike widths, other sizes) runs on the kernel below.
+//
 // Work decomposition as in the general kernel of attention.cu: for one (sequence, kv head) the
 // rows are the pairs (query token, q head of the group), cut into tiles of 16; a block of four
 // warps takes one tile and walks the keys in tiles of 32; warp w owns rows w, w+4, w+8, w+12.
 // With splits > 1 the key tiles are divided among blocks that leave partial results, combined by
 // a second kernel in a fixed order; the sink is counted by the first split.
 #include "common.cuh"
+#include "attention_mma.cuh"
+#include "attention_tc.cuh"
 
 using namespace vapi;
 
@@ -315,6 +323,36 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
     if (splits < 1 || splits > 32) return fail(-1, "masked_attention: %d splits", splits);
     if (splits > 1 && (!part_o || !part_ml)) return fail(-1, "masked_attention: splits need scratch buffers");
     if (page_size <= 0 || num_pages <= 0) return fail(-1, "masked_attention: no pages");
+    if (dtype == VAPI_BF16 && dk == dv && (dk == 64 || dk == 128) && page_size % FA_BK == 0 && q_row_stride % 2 == 0 &&
+        nkv <= 65535 && (long long)num_seqs * splits <= 65535) {
+        // the cache page is [2][nkv][page_size][d] when keys and values have one width: the layout of the fast kernels
+        int rc;
+        const bool tc_ok = dk == FT_HD && splits == 1 && q_row_stride % 8 == 0 && scale > 0.f && max_q >= FT_AUTO_MAX_Q &&
+                           ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0;
+        if (tc_ok) {
+            const int min_q = num_seqs == 1 ? 1 : FT_MIN_Q;
+            rc = launch_flash_tc(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, num_seqs, max_q, nh,
+                                 nkv, page_size, num_pages, scale, window, min_q, status, stream, chunk, sinks, gate, gate_stride);
+            if (rc != 0 || min_q == 1) return rc;
+            return launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                          num_seqs, FT_MIN_Q - 1, nh, nkv, page_size, num_pages, scale, window, 1, status, stream,
+                                          FT_MIN_Q, 0, chunk, sinks, gate, gate_stride);
+        }
+        const bool few_rows = (long long)max_q * (nh / nkv) <= 16;
+#define MA_FLASH(HD, NW)                                                                                                      \
+    rc = launch_flash<HD, NW, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,    \
+                                 num_seqs, max_q, nh, nkv, page_size, num_pages, scale, window, splits, status, stream, 0, 0, \
+                                 chunk, sinks, gate, gate_stride)
+        if (dk == 64) { if (few_rows) MA_FLASH(64, 1); else MA_FLASH(64, 4); }
+        else          { if (few_rows) MA_FLASH(128, 1); else MA_FLASH(128, 4); }
+#undef MA_FLASH
+        if (rc != 0 || splits == 1) return rc;
+        const long long rows = (long long)n * nh;
+        return check_launch("masked_attention_combine",
+                            launch(masked_attention_combine_kernel<__nv_bfloat16>, (int)((rows + 3) / 4), 128, 0, stream,
+                                   (const float*)part_o, (const float*)part_ml, (const __nv_bfloat16*)gate, gate_stride,
+                                   (__nv_bfloat16*)out, rows, nh, dv, splits));
+    }
 #define MA_GO(T, DV) return launch_masked<T, DV>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, sinks, gate, \
                                                  gate_stride, out, part_o, part_ml, n, num_seqs, max_q, nh, nkv, dk, dv,         \
                                                  page_size, num_pages, scale, window, chunk, splits, status, stream)

@@ -57,7 +57,11 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
                    float scale_log2e, int window, int splits, int q_below, int rows_above,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, int mask_chunk = 0, const float* __restrict__ sinks = nullptr,
+                   const __nv_bfloat16* __restrict__ gate = nullptr, long long gate_stride = 0) {
+    // mask_chunk > 0: a query also sees only keys of its own block of mask_chunk positions (counted from
+    // position 0); sinks: exp(sink[head]) joins the softmax's denominator (counted by the first split);
+    // gate: the output of (token, head) is multiplied by sigmoid(gate[token * gate_stride + head])
     // q_below > 0: sequences that bring q_below tokens or more belong to another kernel, and so do
     // sequences of at most rows_above rows (rows_above > 0)
     constexpr int ROWS = NWARPS * 16;
@@ -88,7 +92,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
     const int p_max = base_pos + last_row / n_rep;
-    const int key_lo = window > 0 ? max(0, p_min - window + 1) : 0;
+    int key_lo = window > 0 ? max(0, p_min - window + 1) : 0;
+    if (mask_chunk > 0) key_lo = max(key_lo, (p_min / mask_chunk) * mask_chunk);
     const int kt_lo = key_lo / FA_BK, kt_hi = p_max / FA_BK;
     const int ntiles_all = kt_hi - kt_lo + 1;
     const int chunk = (ntiles_all + splits - 1) / splits;
@@ -97,7 +102,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int nt = max(0, kt_end - kt_begin);
 
     // this thread's two rows: (gq) and (gq + 8) of the warp's 16
-    int row_id[2], row_pos[2], row_tok[2], row_head[2];
+    int row_id[2], row_pos[2], row_tok[2], row_head[2], row_lo[2];
     bool row_ok[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -107,6 +112,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         row_tok[h] = row_ok[h] ? rr / n_rep : 0;
         row_head[h] = g * n_rep + (row_ok[h] ? rr - row_tok[h] * n_rep : 0);
         row_pos[h] = row_ok[h] ? base_pos + row_tok[h] : -1;       // -1: sees nothing
+        row_lo[h] = (mask_chunk > 0 && row_ok[h]) ? (row_pos[h] / mask_chunk) * mask_chunk : 0;
     }
     // lowest / highest position among the warp's 16 rows (for skipping and for mask decisions)
     const int w_first = tile_start + warp * 16;
@@ -191,7 +197,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         const int kt = kt_begin + it;
         const int k0 = kt * FA_BK;
         // a warp none of whose rows reaches this tile (causal) or whose window has passed it skips it
-        if (!warp_has_rows || k0 > w_pos_max || (window > 0 && k0 + FA_BK - 1 <= w_pos_min - window)) continue;
+        if (!warp_has_rows || k0 > w_pos_max || (window > 0 && k0 + FA_BK - 1 <= w_pos_min - window) ||
+            (mask_chunk > 0 && k0 + FA_BK - 1 < (w_pos_min / mask_chunk) * mask_chunk)) continue;
         const __nv_bfloat16* ks = sK + (it % STAGES) * TILE;
         const __nv_bfloat16* vs = sV + (it % STAGES) * TILE;
 
@@ -213,7 +220,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         }
         // scale, mask, online softmax (base 2)
         const bool need_mask = (k0 + FA_BK - 1 > w_pos_min) || (k0 + FA_BK > klen) ||
-                               (window > 0 && k0 <= w_pos_max - window);
+                               (window > 0 && k0 <= w_pos_max - window) ||
+                               (mask_chunk > 0 && k0 < (w_pos_max / mask_chunk) * mask_chunk);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float mx = -INFINITY;
@@ -224,7 +232,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     float v = sc[i][2 * h + e] * scale_log2e;
                     if (need_mask) {
                         const int kj = k0 + i * 8 + 2 * tq + e;
-                        const bool vis = kj <= row_pos[h] && kj < klen && (window <= 0 || kj > row_pos[h] - window);
+                        const bool vis = kj <= row_pos[h] && kj < klen && (window <= 0 || kj > row_pos[h] - window) &&
+                                         kj >= row_lo[h];
                         v = vis ? v : -INFINITY;
                     }
                     sc[i][2 * h + e] = v;
@@ -280,8 +289,18 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         if (!row_ok[h]) continue;
         const size_t grow = (size_t)(q0 + row_tok[h]) * nh + row_head[h];
+        if (sinks && sp == 0) {
+            const float sk = sinks[row_head[h]] * 1.4426950408889634f;       // the running maximum is in base 2
+            const float m_new = fmaxf(m_run[h], sk);
+            const float alpha = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - m_new);
+            l = l * alpha + exp2f(sk - m_new);
+            m_run[h] = m_new;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) { o_acc[i][2 * h] *= alpha; o_acc[i][2 * h + 1] *= alpha; }
+        }
         if (splits == 1) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (gate) inv *= 1.f / (1.f + __expf(-__bfloat162float(gate[(size_t)(q0 + row_tok[h]) * gate_stride + row_head[h]])));
             __nv_bfloat16* o = out + grow * HD;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i) {
@@ -308,7 +327,8 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
                         const int* block_table, int table_stride, const int* cu_q,
                         const int* seqlens_k, void* out, float* part_o, float* part_ml, int num_seqs,
                         int max_q, int nh, int nkv, int page_size, int num_pages, float scale,
-                        int window, int splits, int* status, cudaStream_t stream, int q_below = 0, int rows_above = 0) {
+                        int window, int splits, int* status, cudaStream_t stream, int q_below = 0, int rows_above = 0,
+                        int mask_chunk = 0, const float* sinks = nullptr, const void* gate = nullptr, long long gate_stride = 0) {
     const int n_rep = nh / nkv;
     const long long max_rows = (long long)max_q * n_rep;
     const long long tiles = (max_rows + NWARPS * 16 - 1) / (NWARPS * 16);
@@ -325,7 +345,8 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
     return check_launch("paged_attention (tensor-core)", launch(kern, grid, NWARPS * 32, smem, stream,
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)cache, block_table, table_stride, cu_q,
         seqlens_k, (__nv_bfloat16*)out, part_o, part_ml, nh, nkv, page_size, num_pages,
-        scale * 1.4426950408889634f, window, splits, q_below, rows_above, status));
+        scale * 1.4426950408889634f, window, splits, q_below, rows_above, status, mask_chunk, sinks,
+        (const __nv_bfloat16*)gate, gate_stride));
 }
 
 }  // namespace vapi

@@ -54,6 +54,13 @@ struct FaTcParams {
     float scale_log2e;
     int window, min_q;
     int* status;
+    // mask_chunk > 0: a query also sees only keys of its own block of mask_chunk positions; sinks: exp(sink[head])
+    // joins the softmax's denominator; gate: the output of (token, head) is multiplied by
+    // sigmoid(gate[token * gate_stride + head])
+    int mask_chunk;
+    const float* sinks;
+    const __nv_bfloat16* gate;
+    long long gate_stride;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -89,7 +96,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
     const int p_max = base_pos + last_row / n_rep;
-    const int key_lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
+    int key_lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
+    if (p.mask_chunk > 0) key_lo = max(key_lo, (p_min / p.mask_chunk) * p.mask_chunk);
     const int kt_lo = key_lo / FT_BK, kt_hi = p_max / FT_BK;
     const int nt = kt_hi - kt_lo + 1;
 
@@ -192,6 +200,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
         const int tok = row_ok ? rr / n_rep : 0;
         const int head = g * n_rep + (row_ok ? rr - tok * n_rep : 0);
         const int pos = row_ok ? base_pos + tok : -1;               // -1: sees nothing
+        const int pos_lo = (p.mask_chunk > 0 && row_ok) ? (pos / p.mask_chunk) * p.mask_chunk : 0;
         const bool partial = tile_start + FT_ROWS > rows_total;
         pdl_wait();                                                 // q was rotated by the kernel before this one
         {
@@ -228,7 +237,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
             mbar_arrive(s_free + 8 * sb);                           // the scores are in registers
 
             const bool need_mask = partial || (k0 + FT_BK - 1 > p_min) || (k0 + FT_BK > klen) ||
-                                   (p.window > 0 && k0 <= p_max - p.window);
+                                   (p.window > 0 && k0 <= p_max - p.window) ||
+                                   (p.mask_chunk > 0 && k0 < (p_max / p.mask_chunk) * p.mask_chunk);
             // (four running maxima and, below, four running sums: a single chain of 64 dependent
             // operations would leave the few warps of an SM waiting on latency)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -236,7 +246,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
 #pragma unroll
                 for (int e = 0; e < FT_BK; ++e) {
                     const int kj = k0 + e;
-                    const bool vis = kj <= pos && kj < klen && (p.window <= 0 || kj > pos - p.window);
+                    const bool vis = kj <= pos && kj < klen && (p.window <= 0 || kj > pos - p.window) && kj >= pos_lo;
                     sv[e] = vis ? sv[e] : -INFINITY;
                     mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
                 }
@@ -299,7 +309,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
         if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done + 8 * ((nt - 1) & 1), ((nt - 1) >> 1) & 1))) ok = false;
         tc5_fence_after();
         if (ok) {                                                   // (uniform over the warp)
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            if (p.sinks && m_run != -INFINITY) l_run += exp2f(p.sinks[head] * 1.4426950408889634f - m_run);
+            float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            if (p.gate) inv *= 1.f / (1.f + __expf(-__bfloat162float(p.gate[(size_t)(q0 + tok) * p.gate_stride + head])));
             __nv_bfloat16* o = p.out + ((size_t)(q0 + tok) * p.nh + head) * FT_HD;
 #pragma unroll
             for (int j = 0; j < FT_HD / 16; ++j) {
@@ -349,7 +361,8 @@ static int make_kv_map(CUtensorMap* map, const void* cache, long long rows) {
 static int launch_flash_tc(const void* q, long long q_row_stride, const void* cache, const int* block_table,
                            int table_stride, const int* cu_q, const int* seqlens_k, void* out, int num_seqs,
                            int max_q, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-                           int min_q, int* status, cudaStream_t stream) {
+                           int min_q, int* status, cudaStream_t stream, int mask_chunk = 0, const float* sinks = nullptr,
+                           const void* gate = nullptr, long long gate_stride = 0) {
     const int n_rep = nh / nkv;
     const long long tiles = ((long long)max_q * n_rep + FT_ROWS - 1) / FT_ROWS;
     if (tiles > 0x7fffffffLL || nkv > 65535 || num_seqs > 65535)
@@ -370,6 +383,7 @@ static int launch_flash_tc(const void* q, long long q_row_stride, const void* ca
     p.q = (const __nv_bfloat16*)q; p.q_row_stride = q_row_stride; p.block_table = block_table; p.table_stride = table_stride;
     p.cu_q = cu_q; p.seqlens_k = seqlens_k; p.out = (__nv_bfloat16*)out; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
     p.num_pages = num_pages; p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.min_q = min_q; p.status = status;
+    p.mask_chunk = mask_chunk; p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
     dim3 grid((unsigned)tiles, nkv, num_seqs);
     return check_launch("paged_attention (tcgen05)", launch(flash_tc_kernel, grid, FT_THREADS, FT_SMEM, stream, map, p));
 }

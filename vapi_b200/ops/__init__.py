@@ -1176,7 +1176,8 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table), block_table.stride(0), _p(cu_q),
         _p(seqlens_k), _p(sinks), _p(gate), ctypes.c_longlong(gate_stride), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, dk, dv, int(page_size), cache_layer.shape[0], ctypes.c_float(scale), int(window), int(chunk),
-        int(splits), _p(status), _stream()), 2 if splits > 1 else 1)
+        int(splits), _p(status), _stream()),
+        2 if splits > 1 or (q.dtype == torch.bfloat16 and dk == dv == 64 and max_q >= 64 and num_seqs > 1) else 1)
     return out
 
 
