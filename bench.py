@@ -181,7 +181,10 @@ OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens
        "skinny_linear": "gemv", "skinny_shortconv": "gemv", "linear_tc": "linear_tc", "prompt_linear": "linear_prompt",
        "rope_cos_sin": "rope",
        "qk_norm_rope_write": "rope", "paged_attention": "attention", "decode_attention_fused": "attention",
-       "shortconv": "shortconv", "sample_rows": "sampling", "sample_truncated": "sampling", "linear": "library"}
+       "shortconv": "shortconv", "sample_rows": "sampling", "sample_truncated": "sampling", "linear": "library",
+       "postnorm_add_rmsnorm": "elementwise", "gated_group_rmsnorm": "elementwise", "scale_rows": "elementwise",
+       "rope_cos_sin_scaled": "rope", "qk_norm_rope_write_split": "rope", "masked_attention": "attention_masked",
+       "causal_conv_silu": "recurrent", "gated_delta": "recurrent", "state_space": "recurrent"}
 
 
 class OpLog:
@@ -301,6 +304,8 @@ def run(args):
     layers = args.layers or full_layers
     if args.only == "serve":
         return serve(args, cfg)
+    if args.only == "mixers":
+        return mixers(args)
     if layers != full_layers:
         cfg["num_hidden_layers"] = layers
         cfg["layer_types"] = cfg["layer_types"][:layers]
@@ -718,6 +723,165 @@ def measure_prefill(runner, ops, mm_params, pk, peak_tflops, gen, vocab, dev, wa
     return prefill, fam_out
 
 
+def vukavik_sizes(name):
+    """Vukavik layers at the widths of LFM2-<name>: attention with the same heads as the LFM2 stack
+    (keys and values of 64, chunks of 8,192, YaRN-scaled rotation), the gated delta rule with heads of
+    128 x 128 across the width, Mamba-2 with twice the width inside (heads of 64, state 128), a dense
+    feed-forward of the LFM2 stack's width behind every mixer; eight layers."""
+    from vapi_b200.models.lfm2 import Lfm2Config
+    lf = lfm2_sizes(name)
+    W, ff = lf["hidden_size"], Lfm2Config.effective_ff_dim(lf)
+    mlp = {"kind": "dense", "ff": ff}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": lf["num_attention_heads"], "kv_heads": lf["num_key_value_heads"], "dim": 64, "vdim": 64, "scale": 0.125,
+        "mask": {"size": 8192}, "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    dl = {"type": "delta", "mlp": mlp, "mixer": {"heads": W // 128, "kv_heads": W // 128, "dim": 128, "vdim": 128, "conv": 4}}
+    mb = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    vk = {"architecture": "Vukavik", "vocab": lf["vocab_size"], "width": W, "residual_mult": 0.5, "logit_scale": 1.0,
+          "norm": {"eps": 1e-5}, "layers": [dl, mb, dl, att, dl, mb, dl, att]}
+    lf = dict(lf, num_hidden_layers=8, layer_types=["conv", "conv", "conv", "full_attention"] * 2)
+    return vk, lf
+
+
+def mixers(args):
+    """``--only mixers``: prefill and decode of Vukavik layers beside LFM2 layers of equal width (random
+    weights, eight layers each), and where each model's time goes, kernel family by kernel family."""
+    import torch
+    from vapi_b200 import ops
+    from vapi_b200.engine.runner import ModelRunner
+    from vapi_b200.engine.step import StepEntry
+    pk = peaks()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    T, B, ctx_len, page = 2048, args.batch, min(args.context, 4096), args.page_size or ModelRunner.default_page_size
+    gen = torch.Generator().manual_seed(1)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    out = {"only": "mixers", "sizes": args.sizes, "dtype": "bfloat16", "prefill_tokens": T, "decode_batch": B,
+           "decode_context": ctx_len, "peaks": pk, "models": {}}
+    vk, lf = vukavik_sizes(args.sizes)
+    for name, cfg in (("vukavik", vk), ("lfm2", lf)):
+        vocab = cfg.get("vocab") or cfg["vocab_size"]
+        n_pages = (B + 1) * (-(-(ctx_len + 64) // page)) + 8
+        runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=n_pages, page_size=page,
+                                         max_requests=max(B, 8), max_batched_tokens=8192, max_context=ctx_len + 64,
+                                         watermark=0.0, validate=False)
+        wbytes, mm_params = model_numbers(runner)
+
+        def prefill(tag, log=None):
+            rc = runner.cache.open(("p", tag))
+            toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
+            assert runner.cache.reserve(rc, T)
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            runner.step([StepEntry(rc, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.cache.close(rc)
+            return e0.elapsed_time(e1)
+
+        times = [prefill(i) for i in range(3 + 5)][3:]
+        pre_ms = sorted(times)[len(times) // 2]
+        with OpLog(ops, runner.plan, events=True) as log:
+            prefill("families")
+        torch.cuda.synchronize()
+        fam = {}
+        for c in log.calls:
+            f = fam.setdefault(family_of(c), {"ms": 0.0, "calls": 0, "flops": 0.0, "bytes": 0})
+            f["ms"] += c["events"][0].elapsed_time(c["events"][1])
+            f["calls"] += 1
+            if c["op"] in PRODUCTS and c["weight_shape"]:
+                f["flops"] += 2.0 * c["rows"] * c["weight_shape"][0] * c["weight_shape"][1]
+            else:
+                f["bytes"] += c["moved_bytes"]
+        # arithmetic of the mixers' own kernels for one prompt of T tokens, per call
+        mix_flops = {}
+        for blk in runner.plan.layers:
+            m = blk.mixer
+            kind = type(m).__name__
+            if kind == "GQAttention":
+                span = min(T, m.chunk) if getattr(m, "chunk", 0) else T
+                pairs = (T // span) * span * (span + 1) / 2 + (T % span) * (T % span + 1) / 2
+                mix_flops["masked_attention" if getattr(m, "general", False) else "paged_attention"] = 2.0 * m.nh * (m.d + getattr(m, "dv", m.d)) * pairs
+            elif kind == "GatedDeltaMixer":
+                mix_flops["gated_delta"] = 2.0 * 4 * m.nh * m.dk * m.dv * T      # decay, S^T k, the rank-one write, S^T q
+            elif kind == "Mamba2Mixer":
+                mix_flops["state_space"] = 2.0 * 3 * m.nh * m.N * m.p * T        # decay, the rank-one write, S^T C
+        rows = {}
+        for k, f in sorted(fam.items(), key=lambda kv: -kv[1]["ms"]):
+            row = {"ms": round(f["ms"], 3), "calls": f["calls"]}
+            if f["flops"]:
+                tf = f["flops"] / (f["ms"] / 1e3) / 1e12
+                row.update(tflops=round(tf, 1), frac_bf16_peak=round(tf / pk["bf16_tflops"], 3))
+            elif k in mix_flops:
+                tf = mix_flops[k] * f["calls"] / (f["ms"] / 1e3) / 1e12
+                row.update(tflops=round(tf, 2))
+                if "attention" in k:
+                    row.update(frac_bf16_peak=round(tf / pk["bf16_tflops"], 4))
+            if not f["flops"] and f["bytes"]:
+                gb = f["bytes"] / (f["ms"] / 1e3) / 1e9
+                row.update(GBps=round(gb, 0), frac_hbm=round(gb / pk["hbm_gbs"], 3))
+            rows[k] = row
+        # decode: B requests at ctx_len, captured steps
+        rcs = []
+        start = ctx_len - args.steps - 1
+        for i in range(B):
+            rc = runner.cache.open(("d", i))
+            toks = torch.randint(0, vocab, (start,), generator=gen).tolist()
+            pos = 0
+            while pos < start:
+                q = min(2048, start - pos)
+                assert runner.cache.reserve(rc, pos + q)
+                runner.step([StepEntry(rc, toks[pos:pos + q], [])])
+                pos += q
+            rcs.append(rc)
+
+        def decode(count):
+            toks = torch.randint(0, vocab, (count, B), generator=gen).tolist()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            before = ops.launch_count
+            e0.record()
+            for s_ in range(count):
+                entries = []
+                for j, rc in enumerate(rcs):
+                    assert runner.cache.reserve(rc, rc.num_tokens + 1)
+                    entries.append(StepEntry(rc, [toks[s_][j]], [0]))
+                logits = runner.step_decode_graph(entries)
+                if logits is None:
+                    logits = runner.step(entries)
+                ops.sample_rows(logits)
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1), ops.launch_count - before
+
+        regions = []
+        for it in range(2 + 5):
+            ms, launches = decode(args.steps)
+            for rc in rcs:
+                runner.cache.commit(rc, start)
+            if it >= 2:
+                regions.append(ms)
+        dec_ms = sorted(regions)[len(regions) // 2] / args.steps
+        kv_bytes = B * ctx_len * runner.cache.bytes_per_token() + B * runner.cache.state_bytes_per_request()
+        for rc in rcs:
+            runner.cache.close(rc)
+        out["models"][name] = {
+            "weights_GB": round(wbytes / 1e9, 3),
+            "prefill": {"ms": round(pre_ms, 3), "tokens_per_s": round(T / (pre_ms / 1e3), 0),
+                        "matrix_tflops": round(2.0 * mm_params * T / (pre_ms / 1e3) / 1e12, 1)},
+            "decode": {"ms_per_step": round(dec_ms, 4), "tokens_per_s": round(B / (dec_ms / 1e3), 0),
+                       "launches_per_step": launches // args.steps,
+                       "frac_hbm": round((wbytes + kv_bytes) / (dec_ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)},
+            "prefill_kernels": rows}
+        print(f"[bench] {name}: prefill {pre_ms:.3f} ms, decode {dec_ms:.4f} ms/step", file=sys.stderr, flush=True)
+        del runner
+        torch.cuda.empty_cache()
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def reference_arm():
     """The reference is a Rust workspace (Cargo, candle); it has no Python package to
     install and no Rust toolchain exists here, so its arm cannot run."""
@@ -737,11 +901,12 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--impl", default="vapi_b200", choices=["vapi_b200", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "serve", "trace"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "serve", "trace", "mixers"],
                     help="run just the headline decode point, just the prefill, (serve) continuous "
                          "batching of --requests requests with random prompt lengths through the engine loop, or "
                          "(trace) a few decode steps of a measuring build whose kernels stamp the device clock, "
-                         "and print what one step's kernels did inside the captured graph")
+                         "and print what one step's kernels did inside the captured graph, or (mixers) prefill and "
+                         "decode of eight Vukavik layers beside eight LFM2 layers of equal width, kernel family by kernel family")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
     ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--dtype", default="bfloat16", help="bfloat16 (serving) or float32 (the true 32-bit path)")
