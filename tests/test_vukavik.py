@@ -342,12 +342,14 @@ def test_norm_kernels_of_the_blocks_and_the_gated_group_norm(dtype):
     xr = x.clone()
     plain_ops.postnorm_add_rmsnorm(xr, y, wp, 1e-5, 0.3, None, 0.0, dtype)
     assert torch.allclose(xd.cpu(), xr, atol=1e-5)
-    yy, z = torch.randn((n, 120), generator=g) * 2, torch.randn((n, 131), generator=g).to(dtype)
-    for group, wlen, first in ((40, 40, False), (60, 120, True), (120, 120, True), (24, 24, False)):
-        wv = torch.randn(wlen, generator=g)
-        want = plain_ops.gated_group_rmsnorm(yy, z[:, 4:124], wv, 1e-5, group, first, dtype)
-        got = ops.gated_group_rmsnorm(yy.cuda(), z.cuda()[:, 4:124], wv.cuda(), 1e-5, group, first, dtype)
-        assert torch.allclose(got.float().cpu(), want.float(), atol=tol, rtol=tol), (group, wlen, first)
+    for width, cases in ((120, ((40, 40, False), (60, 120, True), (120, 120, True), (24, 24, False))),
+                         (2400, ((1200, 2400, True), (600, 600, False), (2400, 2400, True)))):      # wide groups: a block each
+        yy, z = torch.randn((n, width), generator=g) * 2, torch.randn((n, width + 11), generator=g).to(dtype)
+        for group, wlen, first in cases:
+            wv = torch.randn(wlen, generator=g)
+            want = plain_ops.gated_group_rmsnorm(yy, z[:, 4:4 + width], wv, 1e-5, group, first, dtype)
+            got = ops.gated_group_rmsnorm(yy.cuda(), z.cuda()[:, 4:4 + width], wv.cuda(), 1e-5, group, first, dtype)
+            assert torch.allclose(got.float().cpu(), want.float(), atol=tol, rtol=tol), (group, wlen, first)
 
 
 @pytest.mark.gpu

@@ -482,6 +482,38 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     }
 }
 
+// The same for wide groups (a whole row of a few thousand columns is one group): a block per (row, group).
+template <typename T>
+__global__ void gated_group_rmsnorm_wide_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
+                                                const float* __restrict__ w, int w_len, float eps, int gate_first,
+                                                T* __restrict__ out, int n, int width, int group) {
+    __shared__ float red[33];
+    const int groups = width / group;
+    const int t = blockIdx.x / groups, g = blockIdx.x - t * groups;
+    pdl_trigger();
+    pdl_wait();
+    const float* yr = y + (size_t)t * width + (size_t)g * group;
+    const T* zr = z + (size_t)t * z_stride + (size_t)g * group;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < group; c += blockDim.x) {
+        float v = yr[c];
+        if (gate_first) {
+            const float zv = to_f32(zr[c]);
+            v *= zv / (1.f + expf(-zv));
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)group + eps);
+    T* orow = out + (size_t)t * width + (size_t)g * group;
+    for (int c = threadIdx.x; c < group; c += blockDim.x) {
+        const float zv = to_f32(zr[c]);
+        const float gate = zv / (1.f + expf(-zv));
+        const float wv = w[(g * group + c) % w_len];
+        orow[c] = from_f32<T>(gate_first ? (yr[c] * gate) * inv * wv : yr[c] * inv * wv * gate);
+    }
+}
+
 VAPI_EXPORT int vapi_gated_group_rmsnorm(const float* y, const void* z, long long z_stride, int dtype, const float* w,
                                          int w_len, float eps, int gate_first, void* out, int n, int width, int group,
                                          cudaStream_t stream) {
@@ -492,6 +524,16 @@ VAPI_EXPORT int vapi_gated_group_rmsnorm(const float* y, const void* z, long lon
     const int warps = 4;
     const int blocks = (int)((items + warps - 1) / warps);
     cudaError_t e;
+    if (group >= 512 && items <= 0x7fffffffLL && (dtype == VAPI_F32 || dtype == VAPI_BF16)) {
+        const int threads = group >= 2048 ? 256 : 128;
+        if (dtype == VAPI_F32)
+            e = launch(gated_group_rmsnorm_wide_kernel<float>, (int)items, threads, 0, stream, y, (const float*)z, z_stride, w,
+                       w_len, eps, gate_first, (float*)out, n, width, group);
+        else
+            e = launch(gated_group_rmsnorm_wide_kernel<__nv_bfloat16>, (int)items, threads, 0, stream, y, (const __nv_bfloat16*)z,
+                       z_stride, w, w_len, eps, gate_first, (__nv_bfloat16*)out, n, width, group);
+        return check_launch("gated_group_rmsnorm", e);
+    }
     if (dtype == VAPI_F32)
         e = launch(gated_group_rmsnorm_kernel<float>, blocks, warps * 32, 0, stream, y, (const float*)z, z_stride, w, w_len, eps,
                    gate_first, (float*)out, n, width, group);

@@ -535,6 +535,9 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
             and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.shape[0] % 16 == 0
             and weight.is_contiguous() and x.is_contiguous()):
         return prompt_linear(weight, act=x, epilogue="swiglu")
+    if (x.dtype == torch.bfloat16 and x.is_contiguous() and weight.shape[0] % 16 == 0 and rows <= TC_MAX_ROWS
+            and few_rows_applies(rows, weight)):
+        return few_rows_linear(weight, act=x, epilogue="swiglu")      # a decode step: SwiGLU rides on the product
     return swiglu(linear(x, weight))
 
 
