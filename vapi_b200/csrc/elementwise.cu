@@ -424,6 +424,65 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __re
     }
 }
 
+// The same with 16-byte accesses and the row held in registers between the passes (hidden a multiple
+// of 4, at most 4 * NORM_KMAX * blockDim elements): x, y and the weights are read once, x and the
+// output written once.
+template <typename T>
+__global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ y,
+                                                const float* __restrict__ w_post, float eps_post, float mult,
+                                                const float* __restrict__ w, float eps,
+                                                const int* __restrict__ rows, T* __restrict__ out,
+                                                int n_out, int hidden, int write_x) {
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (j >= n_out) return;
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * hidden;
+    const T* yr = y + (size_t)row * hidden;
+    const int h4 = hidden >> 2;
+    float4 v[NORM_KMAX];
+    float ssy = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < h4) {
+            v[k] = Pack4<T>::load(yr + 4 * c);
+            ssy += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    ssy = block_sum(ssy, red);
+    const float inv_y = rsqrtf(ssy / (float)hidden + eps_post);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < h4) {
+            const float4 xv = Pack4<float>::load(xr + 4 * c), wp = Pack4<float>::load(w_post + 4 * c);
+            v[k].x = xv.x + mult * (v[k].x * inv_y * wp.x);
+            v[k].y = xv.y + mult * (v[k].y * inv_y * wp.y);
+            v[k].z = xv.z + mult * (v[k].z * inv_y * wp.z);
+            v[k].w = xv.w + mult * (v[k].w * inv_y * wp.w);
+            if (write_x) Pack4<float>::store(xr + 4 * c, v[k]);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    if (!w) return;
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    T* orow = out + (size_t)j * hidden;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < h4) {
+            const float4 wv = Pack4<float>::load(w + 4 * c);
+            Pack4<T>::store(orow + 4 * c, make_float4(v[k].x * inv * wv.x, v[k].y * inv * wv.y, v[k].z * inv * wv.z, v[k].w * inv * wv.w));
+        }
+    }
+}
+
 VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, const float* w_post, float eps_post,
                                           float mult, const float* w, float eps, const int* rows, void* out,
                                           int n_out, int hidden, cudaStream_t stream) {
@@ -433,6 +492,18 @@ VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, co
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int write_x = rows ? 0 : 1;
     cudaError_t e;
+    if (hidden % 4 == 0 && (dtype == VAPI_F32 || dtype == VAPI_BF16) && mult != 0.f) {
+        const int vt = hidden >= 1024 ? 256 : 128;
+        if (hidden / 4 <= NORM_KMAX * vt) {
+            if (dtype == VAPI_F32)
+                e = launch(postnorm_add_rmsnorm_vec_kernel<float>, n_out, vt, 0, stream, x, (const float*)y, w_post, eps_post,
+                           mult, w, eps, rows, (float*)out, n_out, hidden, write_x);
+            else
+                e = launch(postnorm_add_rmsnorm_vec_kernel<__nv_bfloat16>, n_out, vt, 0, stream, x, (const __nv_bfloat16*)y,
+                           w_post, eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+            return check_launch("postnorm_add_rmsnorm", e);
+        }
+    }
     if (dtype == VAPI_F32)
         e = launch(postnorm_add_rmsnorm_kernel<float>, n_out, threads, 0, stream, x, (const float*)y, w_post, eps_post, mult,
                    w, eps, rows, (float*)out, n_out, hidden, write_x);

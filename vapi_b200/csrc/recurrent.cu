@@ -95,6 +95,85 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long x_str
     out[(size_t)t * channels + c] = from_f32<T>(silu_f(acc));
 }
 
+// The (token, channel) part with 16-byte accesses: a thread takes VEC consecutive channels of one
+// token (8 of bfloat16, 4 of float).  Rows of x, the taps and the output must be 16-byte aligned.
+template <typename T> struct ConvVec;
+template <> struct ConvVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 f = *reinterpret_cast<const float4*>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct ConvVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<unsigned*>(&a);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+template <typename T>
+__global__ void causal_conv_silu_vec_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ taps,
+                                            const float* __restrict__ bias, const int* __restrict__ tok_seq,
+                                            const int* __restrict__ cu_q, T* __restrict__ out, int n, int channels, int L) {
+    constexpr int VEC = ConvVec<T>::N;
+    const int cv = channels / VEC;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    if (item >= (long long)n * cv) {
+        pdl_wait();
+        return;
+    }
+    const int t = (int)(item / cv), c = (int)(item - (long long)t * cv) * VEC;
+    const int i = t - cu_q[tok_seq[t]];
+    if (i < L - 1) {                                        // a head token: the (sequence, channel) blocks' work
+        pdl_wait();
+        return;
+    }
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; e += 4) {
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias) b = *reinterpret_cast<const float4*>(bias + c + e);
+        acc[e] = b.x; acc[e + 1] = b.y; acc[e + 2] = b.z; acc[e + 3] = b.w;
+    }
+    pdl_wait();
+    for (int j = 0; j < L; ++j) {
+        float xv[VEC];
+        ConvVec<T>::load(x + (size_t)(t - (L - 1) + j) * x_stride + c, xv);
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4) {
+            const float4 w = *reinterpret_cast<const float4*>(taps + (size_t)j * channels + c + e);
+            acc[e] = fmaf(w.x, xv[e], acc[e]);
+            acc[e + 1] = fmaf(w.y, xv[e + 1], acc[e + 1]);
+            acc[e + 2] = fmaf(w.z, xv[e + 2], acc[e + 2]);
+            acc[e + 3] = fmaf(w.w, xv[e + 3], acc[e + 3]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+    ConvVec<T>::store(out + (size_t)t * channels + c, acc);
+}
+
 VAPI_EXPORT int vapi_causal_conv_silu(const void* x, long long x_stride, int dtype, const float* taps, const float* bias,
                                       float* state, long long slot_stride, const int* state_slots, const int* tok_seq,
                                       const int* cu_q, const int* positions, void* out, int n, int num_seqs,
@@ -107,6 +186,33 @@ VAPI_EXPORT int vapi_causal_conv_silu(const void* x, long long x_stride, int dty
     const int body_blocks = max_q > L - 1 ? (int)(((long long)n * channels + threads - 1) / threads) : 0;
     if (head_blocks + body_blocks == 0) return 0;
     cudaError_t e;
+    const int vec = dtype == VAPI_BF16 ? 8 : 4;
+    const size_t esz = dtype == VAPI_BF16 ? 2 : 4;
+    if (body_blocks > 0 && (dtype == VAPI_F32 || dtype == VAPI_BF16) && channels % vec == 0 && x_stride % vec == 0 &&
+        ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)taps % 16) == 0 && (!bias || ((uintptr_t)bias % 16) == 0) &&
+        (x_stride * esz) % 16 == 0) {
+        // the portions' first tokens and the states by (sequence, channel) threads, everything else 16 bytes at a time
+        if (head_blocks > 0) {
+            if (dtype == VAPI_F32)
+                e = launch(causal_conv_silu_kernel<float>, head_blocks, threads, 0, stream, (const float*)x, x_stride, taps, bias, state,
+                           slot_stride, state_slots, tok_seq, cu_q, positions, (float*)out, n, num_seqs, channels, L, num_slots,
+                           head_blocks, status);
+            else
+                e = launch(causal_conv_silu_kernel<__nv_bfloat16>, head_blocks, threads, 0, stream, (const __nv_bfloat16*)x, x_stride,
+                           taps, bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, num_seqs,
+                           channels, L, num_slots, head_blocks, status);
+            const int rc = check_launch("causal_conv_silu", e);
+            if (rc != 0) return rc;
+        }
+        const int vblocks = (int)(((long long)n * (channels / vec) + threads - 1) / threads);
+        if (dtype == VAPI_F32)
+            e = launch(causal_conv_silu_vec_kernel<float>, vblocks, threads, 0, stream, (const float*)x, x_stride, taps, bias, tok_seq,
+                       cu_q, (float*)out, n, channels, L);
+        else
+            e = launch(causal_conv_silu_vec_kernel<__nv_bfloat16>, vblocks, threads, 0, stream, (const __nv_bfloat16*)x, x_stride, taps,
+                       bias, tok_seq, cu_q, (__nv_bfloat16*)out, n, channels, L);
+        return check_launch("causal_conv_silu", e);
+    }
     if (dtype == VAPI_F32)
         e = launch(causal_conv_silu_kernel<float>, head_blocks + body_blocks, threads, 0, stream, (const float*)x, x_stride, taps,
                    bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, (float*)out, n, num_seqs, channels, L,
