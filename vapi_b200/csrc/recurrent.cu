@@ -340,10 +340,12 @@ gated_delta_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, i
     float* S_glob = state + (size_t)slot * slot_stride + ((size_t)h * rows) * cols;
     const bool fresh = positions[t0] == 0;
     pdl_wait();
-    float S[RT];
+    float2 S2[RT / 2];                                      // this thread's rows of its column, two floats a register pair
 #pragma unroll
-    for (int r = 0; r < RT; ++r)
-        S[r] = (!fresh && col_ok && r0 + r < rows) ? S_glob[(size_t)(r0 + r) * cols + col] : 0.f;
+    for (int r = 0; r < RT; r += 2) {
+        S2[r / 2].x = (!fresh && col_ok && r0 + r < rows) ? S_glob[(size_t)(r0 + r) * cols + col] : 0.f;
+        S2[r / 2].y = (!fresh && col_ok && r0 + r + 1 < rows) ? S_glob[(size_t)(r0 + r + 1) * cols + col] : 0.f;
+    }
 
     Stage st;
     float a_raw = 0.f, b_raw = 0.f;
@@ -365,7 +367,7 @@ gated_delta_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, i
             sbeta[threadIdx.x] = sigmoid_f(b_raw);
         }
         __syncthreads();
-        if (first + REC_TC < qlen) fetch(first + REC_TC);   // in flight while this round's steps run
+        if (first + REC_TC < qlen) fetch(first + REC_TC);   // in flight while these sixteen steps run
         // sums of squares and the dot product of k and q: eight threads a token, each an eighth of the rows
         {
             const int tt = threadIdx.x >> 3, part = threadIdx.x & 7;
@@ -394,33 +396,38 @@ gated_delta_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, i
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * RPP + sl * Stage::LANE);
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * RPP + sl * Stage::LANE);
             const float gdec = sg[tt];
-            float kc[RT];
-            float ks[2] = {0.f, 0.f}, qs[2] = {0.f, 0.f};
+            const float2 g2 = make_float2(gdec, gdec);
+            float2 kc[RT / 2];
+            float2 ks[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}, qs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int r4 = 0; r4 < RT / 4; ++r4) {
+            for (int r4 = 0; r4 < RT / 4; ++r4) {            // (two floats an instruction: fma.rn.f32x2)
                 const float4 kv = k4[r4], qv = q4[r4];
-                kc[4 * r4] = kv.x; kc[4 * r4 + 1] = kv.y; kc[4 * r4 + 2] = kv.z; kc[4 * r4 + 3] = kv.w;
-                S[4 * r4] *= gdec; S[4 * r4 + 1] *= gdec; S[4 * r4 + 2] *= gdec; S[4 * r4 + 3] *= gdec;
-                ks[0] = fmaf(kv.x, S[4 * r4], ks[0]); ks[1] = fmaf(kv.y, S[4 * r4 + 1], ks[1]);
-                ks[0] = fmaf(kv.z, S[4 * r4 + 2], ks[0]); ks[1] = fmaf(kv.w, S[4 * r4 + 3], ks[1]);
-                qs[0] = fmaf(qv.x, S[4 * r4], qs[0]); qs[1] = fmaf(qv.y, S[4 * r4 + 1], qs[1]);
-                qs[0] = fmaf(qv.z, S[4 * r4 + 2], qs[0]); qs[1] = fmaf(qv.w, S[4 * r4 + 3], qs[1]);
+                kc[2 * r4] = make_float2(kv.x, kv.y);
+                kc[2 * r4 + 1] = make_float2(kv.z, kv.w);
+                S2[2 * r4] = __fmul2_rn(S2[2 * r4], g2);
+                S2[2 * r4 + 1] = __fmul2_rn(S2[2 * r4 + 1], g2);
+                ks[0] = __ffma2_rn(kc[2 * r4], S2[2 * r4], ks[0]);
+                ks[1] = __ffma2_rn(kc[2 * r4 + 1], S2[2 * r4 + 1], ks[1]);
+                qs[0] = __ffma2_rn(make_float2(qv.x, qv.y), S2[2 * r4], qs[0]);
+                qs[1] = __ffma2_rn(make_float2(qv.z, qv.w), S2[2 * r4 + 1], qs[1]);
             }
             // (k and q stay as they came; their unit-norm factors multiply the sums)
             const float k_inv = skinv[tt];
-            const float ksum = lanes_sum<LPC>(ks[0] + ks[1]) * k_inv;
-            const float qsum = lanes_sum<LPC>(qs[0] + qs[1]) * sqinv[tt];
+            const float ksum = lanes_sum<LPC>((ks[0].x + ks[0].y) + (ks[1].x + ks[1].y)) * k_inv;
+            const float qsum = lanes_sum<LPC>((qs[0].x + qs[0].y) + (qs[1].x + qs[1].y)) * sqinv[tt];
             const float u = sbeta[tt] * (sv[tt * CPB + threadIdx.x / LPC] - ksum);
-            const float uk = u * k_inv;
+            const float2 uk = make_float2(u * k_inv, u * k_inv);
 #pragma unroll
-            for (int r = 0; r < RT; ++r) S[r] = fmaf(kc[r], uk, S[r]);
+            for (int r = 0; r < RT / 2; ++r) S2[r] = __ffma2_rn(kc[r], uk, S2[r]);
             if (sl == 0 && col_ok) out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = fmaf(sqk[tt], u, qsum);
         }
     }
     if (col_ok) {
 #pragma unroll
-        for (int r = 0; r < RT; ++r)
-            if (r0 + r < rows) S_glob[(size_t)(r0 + r) * cols + col] = S[r];
+        for (int r = 0; r < RT; r += 2) {
+            if (r0 + r < rows) S_glob[(size_t)(r0 + r) * cols + col] = S2[r / 2].x;
+            if (r0 + r + 1 < rows) S_glob[(size_t)(r0 + r + 1) * cols + col] = S2[r / 2].y;
+        }
     }
 }
 
@@ -460,10 +467,12 @@ state_space_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __r
     float* S_glob = state + (size_t)slot * slot_stride + ((size_t)h * rows) * cols;
     const bool fresh = positions[t0] == 0;
     pdl_wait();
-    float S[RT];
+    float2 S2[RT / 2];
 #pragma unroll
-    for (int r = 0; r < RT; ++r)
-        S[r] = (!fresh && col_ok && r0 + r < rows) ? S_glob[(size_t)(r0 + r) * cols + col] : 0.f;
+    for (int r = 0; r < RT; r += 2) {
+        S2[r / 2].x = (!fresh && col_ok && r0 + r < rows) ? S_glob[(size_t)(r0 + r) * cols + col] : 0.f;
+        S2[r / 2].y = (!fresh && col_ok && r0 + r + 1 < rows) ? S_glob[(size_t)(r0 + r + 1) * cols + col] : 0.f;
+    }
 
     Stage st;
     float dt_raw = 0.f;
@@ -501,24 +510,27 @@ state_space_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __r
             const float dec = sdec[tt];
             const float xv = sx[tt * CPB + threadIdx.x / LPC];
             const float sxv = sstep[tt] * xv;
-            float cs[2] = {0.f, 0.f};
+            const float2 dec2 = make_float2(dec, dec), sx2 = make_float2(sxv, sxv);
+            float2 cs[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int r4 = 0; r4 < RT / 4; ++r4) {
+            for (int r4 = 0; r4 < RT / 4; ++r4) {            // (two floats an instruction: fma.rn.f32x2)
                 const float4 bv = b4[r4], cv = c4[r4];
-                cs[0] = fmaf(cv.x, S[4 * r4], cs[0]); cs[1] = fmaf(cv.y, S[4 * r4 + 1], cs[1]);
-                cs[0] = fmaf(cv.z, S[4 * r4 + 2], cs[0]); cs[1] = fmaf(cv.w, S[4 * r4 + 3], cs[1]);
-                S[4 * r4] = fmaf(dec, S[4 * r4], bv.x * sxv); S[4 * r4 + 1] = fmaf(dec, S[4 * r4 + 1], bv.y * sxv);
-                S[4 * r4 + 2] = fmaf(dec, S[4 * r4 + 2], bv.z * sxv); S[4 * r4 + 3] = fmaf(dec, S[4 * r4 + 3], bv.w * sxv);
+                cs[0] = __ffma2_rn(make_float2(cv.x, cv.y), S2[2 * r4], cs[0]);
+                cs[1] = __ffma2_rn(make_float2(cv.z, cv.w), S2[2 * r4 + 1], cs[1]);
+                S2[2 * r4] = __ffma2_rn(dec2, S2[2 * r4], __fmul2_rn(make_float2(bv.x, bv.y), sx2));
+                S2[2 * r4 + 1] = __ffma2_rn(dec2, S2[2 * r4 + 1], __fmul2_rn(make_float2(bv.z, bv.w), sx2));
             }
-            const float csum = lanes_sum<LPC>(cs[0] + cs[1]);       // C . S before the token's write
+            const float csum = lanes_sum<LPC>((cs[0].x + cs[0].y) + (cs[1].x + cs[1].y));       // C . S before the token's write
             if (sl == 0 && col_ok)
                 out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = fmaf(dec, csum, fmaf(sbc[tt], sxv, skip * xv));
         }
     }
     if (col_ok) {
 #pragma unroll
-        for (int r = 0; r < RT; ++r)
-            if (r0 + r < rows) S_glob[(size_t)(r0 + r) * cols + col] = S[r];
+        for (int r = 0; r < RT; r += 2) {
+            if (r0 + r < rows) S_glob[(size_t)(r0 + r) * cols + col] = S2[r / 2].x;
+            if (r0 + r + 1 < rows) S_glob[(size_t)(r0 + r + 1) * cols + col] = S2[r / 2].y;
+        }
     }
 }
 
