@@ -119,7 +119,8 @@ def run_trace(model_dir: str, dtype: str, tr: Trace, out_dir: str, max_tokens: i
     done = [int(l.split()[1]) for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert done == [s["step"] for s in tr.steps], "every step must be acknowledged in order"
     with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+        cj = json.load(f)
+        vocab = cj["vocab_size"] if "vocab_size" in cj else cj["vocab"]
     out = {}
     for step, rows in tr.rows.items():
         arr = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4")

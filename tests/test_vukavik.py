@@ -399,3 +399,57 @@ def test_greedy_generation_through_the_entry_point(device, name, lens, new, fold
             top = torch.topk(oracle.logits(list(p) + want[:i])[-1], 2).values
             assert float(top[0] - top[1]) < 1e-3, f"prompt of {len(p)}: token {i} differs without a tie"
     llm.runner.cache.check_invariants()
+
+
+# ---- trace replay: the program a user replays a trace with --------------------------------------------------------
+def _trace(cfg):
+    import replay_util as ru
+    reqs = {f"r{i}": vu.prompt(cfg, n, 70 + i) for i, n in enumerate([1, 70, 40, 90, 66])}
+    tr = ru.Trace()
+    ru.whole(tr, "w", reqs["r1"])
+    ru.tail_decode(tr, "t", reqs["r2"], tail=5)
+    ru.portions(tr, "p", reqs["r3"], sizes=[2, 3, 61, 2, 1])
+    mix = {f"m{k}": v for k, v in reqs.items()}
+    ru.mixed(tr, mix, seed=5, decode_tail=3)
+    tokens = {"w": reqs["r1"], "t": reqs["r2"], "p": reqs["r3"], **mix}
+    return tr, tokens
+
+
+def test_trace_replay_bookkeeping_on_the_host(folders, monkeypatch, capsys, tmp_path):
+    import importlib.machinery
+    import importlib.util
+    import io
+    import json
+    import os
+    import sys
+    import replay_util as ru
+    from vapi_b200 import ops
+    for name in plain_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(plain_ops, name))
+    oracle = vu.Oracle(folders["tiny"])
+    tr, tokens = _trace(oracle.cfg)
+    loader = importlib.machinery.SourceFileLoader("trace_run_script", ru.TRACE_RUN)
+    mod = importlib.util.module_from_spec(importlib.util.spec_from_loader("trace_run_script", loader))
+    loader.exec_module(mod)
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in tr.steps)))
+    out_dir = str(tmp_path / "out")
+    rc = mod.main(["--model", folders["tiny"], "--dtype", "float32", "--out", out_dir, "--max-tokens", str(tr.peak_tokens),
+                   "--device", "cpu"])
+    done = [int(l.split()[1]) for l in capsys.readouterr().out.splitlines() if l.startswith("done ")]
+    assert rc == 0 and done == list(range(len(tr.steps)))
+    got = {step: np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(len(rows), oracle.cfg["vocab"])
+           for step, rows in tr.rows.items()}
+    ok, msg = ru.compare(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, "float32")
+    assert ok, msg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_user_runs_it(dtype, folders, tmp_path):
+    import replay_util as ru
+    name = "mixed" if dtype == "float32" else "mixed/bf16"
+    oracle = vu.Oracle(folders[name])
+    tr, tokens = _trace(oracle.cfg)
+    got = ru.run_trace(folders[name], dtype, tr, str(tmp_path / "out"))
+    ok, msg = ru.compare(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, dtype, bf16_frac=0.15)
+    assert ok, msg
