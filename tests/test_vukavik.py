@@ -402,6 +402,19 @@ def test_greedy_generation_through_the_entry_point(device, name, lens, new, fold
 
 
 # ---- trace replay: the program a user replays a trace with --------------------------------------------------------
+def _compare_trace(tr, got, ref, dtype):
+    """Differences of every wanted row as fractions of the logit range, judged as `_check` judges them."""
+    span = max(float(r.max() - r.min()) for r in ref.values())
+    e = np.array([np.abs(got[step][i] - ref[rid][pos].numpy()).max() / span
+                  for step, rows in tr.rows.items() for i, (rid, pos) in enumerate(rows)])
+    assert np.isfinite(e).all()
+    if dtype == "float32":
+        assert e.max() <= vu.limit(dtype), f"worst {e.max():.3e} of the logit range"
+    else:
+        assert e.mean() <= 0.02 and np.percentile(e, 95) <= vu.limit(dtype) and e.max() <= 0.15, \
+            f"mean {e.mean():.3e}, 95th percentile {np.percentile(e, 95):.3e}, worst {e.max():.3e} of the logit range"
+
+
 def _trace(cfg):
     import replay_util as ru
     reqs = {f"r{i}": vu.prompt(cfg, n, 70 + i) for i, n in enumerate([1, 70, 40, 90, 66])}
@@ -439,8 +452,7 @@ def test_trace_replay_bookkeeping_on_the_host(folders, monkeypatch, capsys, tmp_
     assert rc == 0 and done == list(range(len(tr.steps)))
     got = {step: np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(len(rows), oracle.cfg["vocab"])
            for step, rows in tr.rows.items()}
-    ok, msg = ru.compare(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, "float32")
-    assert ok, msg
+    _compare_trace(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, "float32")
 
 
 @pytest.mark.gpu
@@ -451,5 +463,4 @@ def test_trace_replay_as_a_user_runs_it(dtype, folders, tmp_path):
     oracle = vu.Oracle(folders[name])
     tr, tokens = _trace(oracle.cfg)
     got = ru.run_trace(folders[name], dtype, tr, str(tmp_path / "out"))
-    ok, msg = ru.compare(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, dtype, bf16_frac=0.15)
-    assert ok, msg
+    _compare_trace(tr, got, {k: oracle.logits(v).float() for k, v in tokens.items()}, dtype)
