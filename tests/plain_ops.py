@@ -417,7 +417,7 @@ def _softplus(z):
 
 
 def gated_delta(qkv, ab, A_log, dt_bias, state, state_offset, state_slots, cu_q, positions, nh, nkv, dk, dv,
-                norm_eps=1e-6, status=None):
+                norm_eps=1e-6, status=None, max_q=1):
     n = qkv.shape[0]
     out = torch.zeros((n, nh * dv), dtype=torch.float32)
     rep = nh // nkv
@@ -449,7 +449,7 @@ def gated_delta(qkv, ab, A_log, dt_bias, state, state_offset, state_slots, cu_q,
 
 
 def state_space(xbc, dt, A_log, dt_bias, D, state, state_offset, state_slots, cu_q, positions, nh, groups, n_state, head,
-                status=None):
+                status=None, max_q=1):
     n = xbc.shape[0]
     out = torch.zeros((n, nh * head), dtype=torch.float32)
     rep = nh // groups

@@ -117,6 +117,25 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+// The same launch with the attribute only when `early` is set; without it the kernel starts when
+// everything before it has finished.  For kernels of few, long-lived blocks: launched early, beside the
+// tail of the kernel before, their blocks land wherever a place happens to be free, several on one
+// multiprocessor, and stay there.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (early && pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 inline int check_launch(const char* what, cudaError_t e) {
     if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
     return check_launch(what);

@@ -326,7 +326,6 @@ gated_delta_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, i
     const int g = h / (nh / nkv);
     const bool col_ok = col < cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_trigger();
     const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
     if (qlen <= 0) return;
     const int slot = state_slots[s];
@@ -422,6 +421,7 @@ gated_delta_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, i
             if (sl == 0 && col_ok) out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = fmaf(sqk[tt], u, qsum);
         }
     }
+    pdl_trigger();                                          // (the next kernel is let go when the walk is over)
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < RT; r += 2) {
@@ -454,7 +454,6 @@ state_space_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __r
     const int g = h / (nh / groups);
     const bool col_ok = col < cols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_trigger();
     const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
     if (qlen <= 0) return;
     const int slot = state_slots[s];
@@ -525,6 +524,7 @@ state_space_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __r
                 out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = fmaf(dec, csum, fmaf(sbc[tt], sxv, skip * xv));
         }
     }
+    pdl_trigger();                                          // (the next kernel is let go when the walk is over)
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < RT; r += 2) {
@@ -553,20 +553,21 @@ VAPI_EXPORT int vapi_gated_delta(const void* qkv, long long qkv_stride, int q_of
                                  long long ab_stride, int dtype, const float* A_log, const float* dt_bias, float* state,
                                  long long slot_stride, const int* state_slots, const int* cu_q, const int* positions,
                                  float* out, int num_seqs, int nh, int nkv, int rows, int cols, int num_slots,
-                                 float norm_eps, int* status, cudaStream_t stream) {
+                                 float norm_eps, int max_q, int* status, cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv || rows <= 0 || rows > 256 || cols <= 0)
         return fail(-1, "gated_delta: %d heads over %d, state %d x %d (rows up to 256)", nh, nkv, rows, cols);
     const int cpb = REC_THREADS / rec_lpc(rows);
     dim3 grid((cols + cpb - 1) / cpb, nh, num_seqs);
+    const bool early = max_q < REC_TC;                     // decode steps may start beside the kernel before; long walks may not
     cudaError_t e = cudaSuccess;
 #define GD_CALL(RT, LPC)                                                                                                   \
     if (dtype == VAPI_F32)                                                                                                 \
-        e = launch(gated_delta_kernel<float, RT, LPC>, grid, REC_THREADS, 0, stream, (const float*)qkv, qkv_stride, q_off, \
+        e = launch_if(early, gated_delta_kernel<float, RT, LPC>, grid, REC_THREADS, 0, stream, (const float*)qkv, qkv_stride, q_off, \
                    k_off, v_off, (const float*)ab, ab_stride, A_log, dt_bias, state, slot_stride, state_slots, cu_q,       \
                    positions, out, nh, nkv, rows, cols, num_slots, norm_eps, status);                                      \
     else                                                                                                                   \
-        e = launch(gated_delta_kernel<__nv_bfloat16, RT, LPC>, grid, REC_THREADS, 0, stream, (const __nv_bfloat16*)qkv,    \
+        e = launch_if(early, gated_delta_kernel<__nv_bfloat16, RT, LPC>, grid, REC_THREADS, 0, stream, (const __nv_bfloat16*)qkv,    \
                    qkv_stride, q_off, k_off, v_off, (const __nv_bfloat16*)ab, ab_stride, A_log, dt_bias, state,            \
                    slot_stride, state_slots, cu_q, positions, out, nh, nkv, rows, cols, num_slots, norm_eps, status)
     if (dtype != VAPI_F32 && dtype != VAPI_BF16) return fail(-2, "gated_delta: unsupported dtype %d", dtype);
@@ -579,20 +580,21 @@ VAPI_EXPORT int vapi_state_space(const void* xbc, long long xbc_stride, const vo
                                  const float* A_log, const float* dt_bias, const float* D, float* state,
                                  long long slot_stride, const int* state_slots, const int* cu_q, const int* positions,
                                  float* out, int num_seqs, int nh, int groups, int rows, int cols, int num_slots,
-                                 int* status, cudaStream_t stream) {
+                                 int max_q, int* status, cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (nh <= 0 || groups <= 0 || nh % groups || rows <= 0 || rows > 256 || cols <= 0)
         return fail(-1, "state_space: %d heads over %d groups, state %d x %d (rows up to 256)", nh, groups, rows, cols);
     const int cpb = REC_THREADS / rec_lpc(rows);
     dim3 grid((cols + cpb - 1) / cpb, nh, num_seqs);
+    const bool early = max_q < REC_TC;
     cudaError_t e = cudaSuccess;
 #define SS_CALL(RT, LPC)                                                                                                  \
     if (dtype == VAPI_F32)                                                                                                \
-        e = launch(state_space_kernel<float, RT, LPC>, grid, REC_THREADS, 0, stream, (const float*)xbc, xbc_stride,       \
+        e = launch_if(early, state_space_kernel<float, RT, LPC>, grid, REC_THREADS, 0, stream, (const float*)xbc, xbc_stride,       \
                    (const float*)dt, dt_stride, A_log, dt_bias, D, state, slot_stride, state_slots, cu_q, positions, out, \
                    nh, groups, rows, cols, num_slots, status);                                                            \
     else                                                                                                                  \
-        e = launch(state_space_kernel<__nv_bfloat16, RT, LPC>, grid, REC_THREADS, 0, stream, (const __nv_bfloat16*)xbc,   \
+        e = launch_if(early, state_space_kernel<__nv_bfloat16, RT, LPC>, grid, REC_THREADS, 0, stream, (const __nv_bfloat16*)xbc,   \
                    xbc_stride, (const __nv_bfloat16*)dt, dt_stride, A_log, dt_bias, D, state, slot_stride, state_slots,   \
                    cu_q, positions, out, nh, groups, rows, cols, num_slots, status)
     if (dtype != VAPI_F32 && dtype != VAPI_BF16) return fail(-2, "state_space: unsupported dtype %d", dtype);

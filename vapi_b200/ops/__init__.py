@@ -1216,14 +1216,17 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.T
 
 def gated_delta(qkv: torch.Tensor, ab: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
                 state_offset: int, state_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor, nh: int,
-                nkv: int, dk: int, dv: int, norm_eps: float = 1e-6, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                nkv: int, dk: int, dv: int, norm_eps: float = 1e-6, status: Optional[torch.Tensor] = None,
+                max_q: int = 1 << 30) -> torch.Tensor:
     """The gated delta rule over every sequence of the step.  ``qkv`` [n, 2*nkv*dk + nh*dv] holds q
     heads, k heads (``nkv`` of ``dk``) and v heads (``nh`` of ``dv``); ``ab`` [n, 2*nh] (unit inner
     stride, any row stride) holds the decay's pre-activation a and the write strength's
     pre-activation b.  Per head: q, k made unit vectors (``norm_eps`` inside the root; q also times
     dk^-1/2); ``S <- g S; u = sigmoid(b) (v - S^T k); S <- S + k u^T; o = S^T q`` with
     ``g = exp(-exp(A_log) softplus(a + dt_bias))``.  ``state`` [slots, >= state_offset + nh*dk*dv]
-    float32 carries S [nh, dk, dv] at ``state_offset``.  Returns o [n, nh*dv] float32."""
+    float32 carries S [nh, dk, dv] at ``state_offset``.  ``max_q``: the step's longest portion, when known (a
+    decode step's kernel may start beside the tail of the kernel before it; a long walk starts on an empty
+    device, where its few blocks spread evenly).  Returns o [n, nh*dv] float32."""
     _cuda(qkv, ab, A_log, dt_bias, state, state_slots, cu_q, positions)
     _contig(qkv, "qkv")
     _f32(A_log, "A_log")
@@ -1243,19 +1246,20 @@ def gated_delta(qkv: torch.Tensor, ab: torch.Tensor, A_log: torch.Tensor, dt_bia
         _p(qkv), ctypes.c_longlong(qkv.stride(0)), 0, nkv * dk, 2 * nkv * dk, _p(ab), ctypes.c_longlong(ab.stride(0)),
         _dt(qkv), _p(A_log), _p(dt_bias), ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)),
         ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, nkv,
-        dk, dv, state.shape[0], ctypes.c_float(norm_eps), _p(status), _stream()))
+        dk, dv, state.shape[0], ctypes.c_float(norm_eps), int(min(max_q, 1 << 30)), _p(status), _stream()))
     return out
 
 
 def state_space(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
                 state: torch.Tensor, state_offset: int, state_slots: torch.Tensor, cu_q: torch.Tensor,
                 positions: torch.Tensor, nh: int, groups: int, n_state: int, head: int,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, max_q: int = 1 << 30) -> torch.Tensor:
     """The selective state-space recurrence of Mamba-2 over every sequence of the step.  ``xbc``
     [n, nh*head + 2*groups*n_state] holds x heads, then B and C per group; ``dt`` [n, nh] (unit inner
     stride, any row stride) the step sizes' pre-activations.  Per head, with
     ``step = softplus(dt + dt_bias)``: ``S <- exp(-exp(A_log) step) S + step B x^T; y = S^T C + D x``.
-    ``state`` carries S [nh, n_state, head] float32 at ``state_offset``.  Returns y [n, nh*head] float32."""
+    ``state`` carries S [nh, n_state, head] float32 at ``state_offset``.  ``max_q`` as for :func:`gated_delta`.
+    Returns y [n, nh*head] float32."""
     _cuda(xbc, dt, A_log, dt_bias, D, state, state_slots, cu_q, positions)
     _contig(xbc, "x|B|C")
     _f32(A_log, "A_log")
@@ -1276,5 +1280,5 @@ def state_space(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bia
         _p(xbc), ctypes.c_longlong(xbc.stride(0)), _p(dt), ctypes.c_longlong(dt.stride(0)), _dt(xbc), _p(A_log),
         _p(dt_bias), _p(D), ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)), ctypes.c_longlong(state.stride(0)),
         _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, groups, n_state, head, state.shape[0],
-        _p(status), _stream()))
+        int(min(max_q, 1 << 30)), _p(status), _stream()))
     return out

@@ -97,7 +97,7 @@ class GatedDeltaMixer(Mixer):
                                    ctx.positions, ctx.max_q, ctx.status)
         o = ops.gated_delta(qkv, h[:, C + vv:C + vv + 2 * nh], self.A_log, self.dt_bias, state, self.conv_elems,
                             ctx.state_slots, ctx.cu_q, ctx.positions, nh, self.nkv, self.dk, self.dv, self.unit_eps,
-                            ctx.status)
+                            ctx.status, max_q=ctx.max_q)
         y = ops.gated_group_rmsnorm(o, h[:, C:C + vv], self.norm_w, self.eps, self.dv, False, h.dtype)
         return ops.linear(y, self.w_o)
 
@@ -171,7 +171,7 @@ class Mamba2Mixer(Mixer):
                                    ctx.cu_q, ctx.positions, ctx.max_q, ctx.status)
         y = ops.state_space(xbc, h[:, inner + C:inner + C + self.nh], self.A_log, self.dt_bias, self.D, state,
                             self.conv_elems, ctx.state_slots, ctx.cu_q, ctx.positions, self.nh, self.G, self.N, self.p,
-                            ctx.status)
+                            ctx.status, max_q=ctx.max_q)
         out = ops.gated_group_rmsnorm(y, h[:, :inner], self.norm_w, self.eps, inner // self.norm_groups, True, h.dtype)
         return ops.linear(out, self.w_o)
 
