@@ -536,8 +536,8 @@ state_space_kernel(const T* __restrict__ xbc, long long xbc_stride, const T* __r
 
 // (RT, LPC) for a number of rows: the smallest product that holds them.  Few lanes per column mean many
 // columns per block, and what a block does once per REC_TC tokens (staging, norms) is shared by all of
-// them: measured at 128 rows and one sequence of 2,048 tokens, 32 lanes per column took 0.88 us a token
-// and 16 lanes 0.45 us against 0.40 us with 8.
+// them: measured at 128 rows and one sequence of 2,048 tokens, 16 lanes per column took 0.36 us a token
+// against 0.31 us with 8 (and 1.0 against 1.6 TB/s of state traffic in decode steps of 64 sequences).
 #define REC_DISPATCH(ROWS, CALL)                                    \
     do {                                                            \
         if ((ROWS) <= 16) { CALL(4, 4); }                           \
