@@ -352,7 +352,7 @@ def masked_attention_splits(num_seqs, max_q, max_k, nh, nkv):
 
 
 def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k,
-                     nh, nkv, dk, dv, scale, *, window=0, chunk=0, sinks=None, gate=None, splits=None, status=None):
+                     nh, nkv, dk, dv, scale, *, window=0, chunk=0, sinks=None, gate=None, splits=None, status=None, keep=0):
     rep = nh // nkv
     out = torch.zeros((n, nh * dv), dtype=torch.float32)
     kpart = nkv * page_size * dk
@@ -361,16 +361,13 @@ def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q,
         qlen = q1 - q0
         for j in range(qlen):
             p = klen - qlen + j
-            lo = 0
-            if window > 0:
-                lo = max(lo, p - window + 1)
-            if chunk > 0:
-                lo = max(lo, (p // chunk) * chunk)
+            seen = [i for i in range(p + 1) if (window <= 0 or i > p - window or i < keep)
+                    and (chunk <= 0 or i >= (p // chunk) * chunk)]
             for h in range(nh):
                 g = h // rep
                 qv = _f(q[q0 + j, h * dk:(h + 1) * dk])
                 ks, vs = [], []
-                for i in range(lo, p + 1):
+                for i in seen:
                     pg, off = int(block_table[s, i // page_size]), i % page_size
                     ks.append(_f(cache_layer[pg, (g * page_size + off) * dk:(g * page_size + off + 1) * dk]))
                     vs.append(_f(cache_layer[pg, kpart + (g * page_size + off) * dv:kpart + (g * page_size + off + 1) * dv]))
@@ -388,6 +385,10 @@ def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q,
 
 
 def causal_conv_silu(x, taps, bias, state, state_slots, tok_seq, cu_q, positions, max_q, status=None):
+    return causal_conv(x, taps, bias, state, state_slots, tok_seq, cu_q, positions, max_q, status, act="silu")
+
+
+def causal_conv(x, taps, bias, state, state_slots, tok_seq, cu_q, positions, max_q, status=None, act="none"):
     n, C = x.shape
     L = taps.shape[0]
     out = torch.zeros((n, C), dtype=torch.float32)
@@ -405,7 +406,7 @@ def causal_conv_silu(x, taps, bias, state, state_slots, tok_seq, cu_q, positions
             acc = torch.zeros(C) if bias is None else bias.clone()
             for k in range(L):
                 acc = acc + taps[k] * hist[len(hist) - L + k]
-            out[r] = acc / (1.0 + torch.exp(-acc))
+            out[r] = acc / (1.0 + torch.exp(-acc)) if act == "silu" else acc
             hist = hist[-(L - 1):] if L > 1 else []
         for j in range(L - 1):
             state[slot, j * C:(j + 1) * C] = hist[j]
@@ -475,8 +476,121 @@ def state_space(xbc, dt, A_log, dt_bias, D, state, state_offset, state_slots, cu
     return out
 
 
+def embed_sinusoid(table, tokens, positions, freq, streams=1, status=None):
+    x = _f(table[tokens.long()])
+    if freq is not None:
+        ang = positions.to(torch.float32)[:, None] * freq[None, :]
+        pe = torch.stack([torch.sin(ang), torch.cos(ang)], -1).reshape(x.shape[0], -1)[:, :x.shape[1]]
+        x = x + pe
+    return x[:, None, :].repeat(1, streams, 1).contiguous()
+
+
+def hyper_read_norm(x, y, mix, write, read, weight, eps, out_dtype, rows=None, kind="layer"):
+    """x [n, S, H]: the pending write (x_t <- sum_s mix[s, t] x_s + write[t] y), then the norm of sum_s read[s] x_s."""
+    n, S, H = x.shape
+    new = x
+    if y is not None:
+        new = torch.einsum("st,nsh->nth", mix.reshape(S, S), x) + write.reshape(1, S, 1) * _f(y)[:, None, :]
+        if rows is None:
+            x.copy_(new)
+    if weight is None:
+        return None
+    src = new if rows is None else new[rows.long()]
+    u = src.sum(1) if read is None else (read.reshape(1, S, 1) * src).sum(1)
+    if kind == "layer":
+        d = u - u.mean(-1, keepdim=True)
+        out = d * torch.rsqrt((d * d).mean(-1, keepdim=True) + eps) * weight
+    else:
+        out = u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * weight
+    return out.to(out_dtype)
+
+
+def branch_rmsnorm_mean(branches, weights, eps, scale):
+    acc = 0
+    for a, w in zip(branches, weights):
+        a = _f(a)
+        acc = acc + a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * w
+    return (acc * scale).to(branches[0].dtype)
+
+
+def sigmoid_gate(y, gate):
+    return (_f(y) * torch.sigmoid(_f(gate))).to(y.dtype)
+
+
+def softcap(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
+def rglru(u, y, w_a, b_a, w_i, b_i, lam, decay_c, state, state_offset, state_slots, cu_q, positions, status=None, max_q=1):
+    n, C = u.shape
+    B = w_a.shape[0]
+    bs = C // B
+    out = torch.zeros((n, C), dtype=torch.float32)
+    sp = _softplus(lam)
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        slot = int(state_slots[s])
+        S = state[slot, state_offset:state_offset + C].clone() if int(positions[r0]) > 0 else torch.zeros(C)
+        for r in range(r0, r1):
+            ur = _f(u[r])
+            ga = torch.cat([_f(w_a[b]) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_a
+            gi = torch.cat([_f(w_i[b]) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_i
+            log_a = -decay_c * torch.sigmoid(ga) * sp
+            a = torch.exp(log_a)
+            S = a * S + torch.sqrt(torch.clamp(1.0 - a * a, min=0.0)) * torch.sigmoid(gi) * ur
+            yr = _f(y[r])
+            out[r] = S * (0.5 * yr * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (yr + 0.044715 * yr ** 3))))
+        state[slot, state_offset:state_offset + C] = S
+    return out.to(u.dtype)
+
+
+def relu_squared(x):
+    return (torch.relu(_f(x)) ** 2).to(x.dtype)
+
+
+def moe_route(h, router, correction, experts, top, groups, keep):
+    n = h.shape[0]
+    outputs = router.shape[0]
+    ids = torch.zeros((n, top), dtype=torch.int32)
+    wts = torch.zeros((n, top), dtype=torch.float32)
+    per = outputs // groups
+    for t in range(n):
+        s = torch.softmax(router @ _f(h[t]), 0)
+        choice = s + correction
+        if groups > 1 and keep < groups:
+            gs = choice.reshape(groups, per).max(1).values
+            kept = sorted(range(groups), key=lambda g: (-float(gs[g]), g))[:keep]
+            for g in range(groups):
+                if g not in kept:
+                    choice[g * per:(g + 1) * per] = -math.inf
+        order = sorted(range(outputs), key=lambda e: (-float(choice[e]), e))[:top]
+        ids[t] = torch.tensor(order, dtype=torch.int32)
+        wts[t] = s[order] / (s[order].sum() + 1e-20)
+    return ids, wts, None
+
+
+def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None):
+    n, W = h.shape
+    experts = 0 if w_up is None else w_up.shape[0]
+    out = torch.zeros((n, W), dtype=torch.float32)
+    for t in range(n):
+        for e, g in zip(ids[t].tolist(), wts[t].tolist()):
+            if e >= experts:
+                out[t] += g * _f(h[t])
+            else:
+                hid = (torch.relu(_f(w_up[e]) @ _f(h[t])) ** 2).to(h.dtype)
+                out[t] += g * (_f(w_down[e]) @ _f(hid))
+    if shared is not None:
+        out += _f(shared)
+    return out.to(h.dtype)
+
+
 ALL = ["embed", "resolve_tokens", "sample_truncated", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties", "postnorm_add_rmsnorm", "gated_group_rmsnorm", "scale_rows", "rope_cos_sin_scaled",
        "qk_norm_rope_write_split", "masked_attention_splits", "masked_attention", "causal_conv_silu", "gated_delta",
-       "state_space"]
+       "state_space", "causal_conv", "embed_sinusoid", "hyper_read_norm", "branch_rmsnorm_mean", "sigmoid_gate", "softcap",
+       "rglru", "relu_squared", "moe_route", "moe_experts"]

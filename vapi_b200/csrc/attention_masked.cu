@@ -5,7 +5,8 @@
 // kernels of attention.cu do not take.
 //
 // A sequence brings len_q queries over len_k keys; query j sits at position p = len_k - len_q + j
-// and sees key i iff  i <= p,  i > p - window (window > 0)  and  floor(i / chunk) = floor(p / chunk)
+// and sees key i iff  i <= p,  (i > p - window  or  i < keep)  (window > 0; keep: the first tokens of a
+// sequence that a window never leaves behind)  and  floor(i / chunk) = floor(p / chunk)
 // (chunk > 0; chunks are counted from position 0 of the sequence).  score = scale * q.k; the
 // softmax's denominator also holds exp(sink_h) when sinks are given (no key, no value, unscaled);
 // head h's output is multiplied by sigmoid(gate[token, h]) when a gate is given.
@@ -47,8 +48,8 @@ template <> struct Ld4<__nv_bfloat16> {
     }
 };
 
-__device__ __forceinline__ bool ma_visible(int j, int p, int klen, int window, int chunk) {
-    return j <= p && j < klen && (window <= 0 || j > p - window) && (chunk <= 0 || j >= (p / chunk) * chunk);
+__device__ __forceinline__ bool ma_visible(int j, int p, int klen, int window, int chunk, int keep) {
+    return j <= p && j < klen && (window <= 0 || j > p - window || j < keep) && (chunk <= 0 || j >= (p / chunk) * chunk);
 }
 
 template <typename T, int DVMAX>
@@ -59,7 +60,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
                         const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int dk, int dv,
                         int page_size, int num_pages, float scale, int window, int chunk, int splits,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, int keep) {
     constexpr int DPL = DVMAX / 32;
     extern __shared__ __align__(16) float smem[];
     const int ldk = dk + 4, ldv = dv + 4;
@@ -82,14 +83,18 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
     const int p_max = base_pos + last_row / n_rep;
-    int key_lo = 0;
+    const int chunk_lo = chunk > 0 ? (p_min / chunk) * chunk : 0;
+    int key_lo = chunk_lo;
     if (window > 0) key_lo = max(key_lo, p_min - window + 1);
-    if (chunk > 0) key_lo = max(key_lo, (p_min / chunk) * chunk);
     const int kt_lo = key_lo / MA_BK, kt_hi = p_max / MA_BK;
-    const int nt = kt_hi - kt_lo + 1;
+    // kept first tokens that the window has left behind: their tiles come before the window's
+    const int keep_hi = (window > 0 && keep > 0) ? min(keep, key_lo) : 0;
+    const int kf_lo = chunk_lo / MA_BK;
+    const int n_first = keep_hi > chunk_lo ? max(0, min((keep_hi + MA_BK - 1) / MA_BK, kt_lo) - kf_lo) : 0;
+    const int nt = n_first + kt_hi - kt_lo + 1;
     const int per = (nt + splits - 1) / splits;
-    const int kt_begin = kt_lo + sp * per;
-    const int kt_end = min(kt_hi + 1, kt_begin + per);
+    const int it_begin = sp * per;
+    const int it_end = min(nt, it_begin + per);
     const size_t page_elems = (size_t)nkv * page_size * (dk + dv);
     const size_t v_base = (size_t)nkv * page_size * dk;
 
@@ -120,13 +125,14 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
     }
 
     const int* bt = block_table + (size_t)s * table_stride;
-    for (int kt = kt_begin; kt < kt_end; ++kt) {
+    for (int it = it_begin; it < it_end; ++it) {
+        const int kt = it < n_first ? kf_lo + it : kt_lo + (it - n_first);
         __syncthreads();
         for (int idx = threadIdx.x; idx < MA_BK * (dk / 4); idx += blockDim.x) {
             const int jj = idx / (dk / 4), c4 = idx - jj * (dk / 4);
             const int j = kt * MA_BK + jj;
             float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (j >= key_lo && j <= p_max && j < klen) {
+            if ((j >= key_lo || (j < keep_hi && j >= chunk_lo)) && j <= p_max && j < klen) {
                 const int page = bt[j / page_size];
                 if (page < 0 || page >= num_pages) {
                     if (status) atomicExch(status, 4);
@@ -140,7 +146,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
             const int jj = idx / (dv / 4), c4 = idx - jj * (dv / 4);
             const int j = kt * MA_BK + jj;
             float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (j >= key_lo && j <= p_max && j < klen) {
+            if ((j >= key_lo || (j < keep_hi && j >= chunk_lo)) && j <= p_max && j < klen) {
                 const int page = bt[j / page_size];
                 if (page >= 0 && page < num_pages)
                     vv = Ld4<T>::load(cache + (size_t)page * page_elems + v_base + ((size_t)g * page_size + (j % page_size)) * dv + c4 * 4);
@@ -170,7 +176,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
 #pragma unroll
         for (int a = 0; a < MA_RPW; ++a) {
             if (!row_ok[a]) continue;
-            const bool vis = ma_visible(j, row_pos[a], klen, window, chunk);
+            const bool vis = ma_visible(j, row_pos[a], klen, window, chunk, keep);
             const float sv = vis ? sc[a] : -INFINITY;
             const float m_new = fmaxf(m[a], warp_max(sv));
             float p = 0.f, alpha = 1.f;
@@ -284,7 +290,7 @@ static int launch_masked(const void* q, long long q_row_stride, const void* cach
                          int table_stride, const int* cu_q, const int* seqlens_k, const float* sinks,
                          const void* gate, long long gate_stride, void* out, float* part_o, float* part_ml, int n,
                          int num_seqs, int max_q, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
-                         float scale, int window, int chunk, int splits, int* status, cudaStream_t stream) {
+                         float scale, int window, int chunk, int splits, int* status, cudaStream_t stream, int keep) {
     const int n_rep = nh / nkv;
     const int tiles = (max_q * n_rep + MA_ROWS - 1) / MA_ROWS;
     const size_t smem = sizeof(float) * ((size_t)(MA_ROWS + MA_BK) * (dk + 4) + (size_t)MA_BK * (dv + 4) +
@@ -299,7 +305,7 @@ static int launch_masked(const void* q, long long q_row_stride, const void* cach
     dim3 grid(tiles, nkv, num_seqs * splits);
     cudaError_t e = launch(kern, grid, MA_WARPS * 32, smem, stream, (const T*)q, q_row_stride, (const T*)cache, block_table,
                            table_stride, cu_q, seqlens_k, sinks, (const T*)gate, gate_stride, (T*)out, part_o, part_ml, nh, nkv,
-                           dk, dv, page_size, num_pages, scale, window, chunk, splits, status);
+                           dk, dv, page_size, num_pages, scale, window, chunk, splits, status, keep);
     int rc = check_launch("masked_attention", e);
     if (rc != 0 || splits == 1) return rc;
     const long long rows = (long long)n * nh;
@@ -314,8 +320,10 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
                                       long long gate_stride, void* out, float* part_o, float* part_ml, int n,
                                       int num_seqs, int max_q, int nh, int nkv, int dk, int dv, int page_size,
                                       int num_pages, float scale, int window, int chunk, int splits, int* status,
-                                      cudaStream_t stream) {
+                                      cudaStream_t stream, int keep) {
     if (n <= 0 || num_seqs <= 0) return 0;
+    if (keep < 0) return fail(-1, "masked_attention: %d kept first tokens", keep);
+    if (window <= 0) keep = 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv) return fail(-1, "masked_attention: %d heads over %d kv heads", nh, nkv);
     if (dk <= 0 || dk % 4 || dv <= 0 || dv % 4 || dv > 256 || dk > 512)
         return fail(-1, "masked_attention: head sizes %d/%d must be multiples of 4 (keys up to 512, values up to 256)", dk, dv);
@@ -332,17 +340,17 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
         if (tc_ok) {
             const int min_q = num_seqs == 1 ? 1 : FT_MIN_Q;
             rc = launch_flash_tc(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, num_seqs, max_q, nh,
-                                 nkv, page_size, num_pages, scale, window, min_q, status, stream, chunk, sinks, gate, gate_stride);
+                                 nkv, page_size, num_pages, scale, window, min_q, status, stream, chunk, sinks, gate, gate_stride, keep);
             if (rc != 0 || min_q == 1) return rc;
             return launch_flash<64, 4, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
                                           num_seqs, FT_MIN_Q - 1, nh, nkv, page_size, num_pages, scale, window, 1, status, stream,
-                                          FT_MIN_Q, 0, chunk, sinks, gate, gate_stride);
+                                          FT_MIN_Q, 0, chunk, sinks, gate, gate_stride, keep);
         }
         const bool few_rows = (long long)max_q * (nh / nkv) <= 16;
 #define MA_FLASH(HD, NW)                                                                                                      \
     rc = launch_flash<HD, NW, 3>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,    \
                                  num_seqs, max_q, nh, nkv, page_size, num_pages, scale, window, splits, status, stream, 0, 0, \
-                                 chunk, sinks, gate, gate_stride)
+                                 chunk, sinks, gate, gate_stride, keep)
         if (dk == 64) { if (few_rows) MA_FLASH(64, 1); else MA_FLASH(64, 4); }
         else          { if (few_rows) MA_FLASH(128, 1); else MA_FLASH(128, 4); }
 #undef MA_FLASH
@@ -355,7 +363,7 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
     }
 #define MA_GO(T, DV) return launch_masked<T, DV>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, sinks, gate, \
                                                  gate_stride, out, part_o, part_ml, n, num_seqs, max_q, nh, nkv, dk, dv,         \
-                                                 page_size, num_pages, scale, window, chunk, splits, status, stream)
+                                                 page_size, num_pages, scale, window, chunk, splits, status, stream, keep)
     if (dtype == VAPI_F32) {
         if (dv <= 64) MA_GO(float, 64);
         if (dv <= 128) MA_GO(float, 128);

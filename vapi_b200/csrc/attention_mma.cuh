@@ -58,7 +58,8 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                    float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
                    float scale_log2e, int window, int splits, int q_below, int rows_above,
                    int* __restrict__ status, int mask_chunk = 0, const float* __restrict__ sinks = nullptr,
-                   const __nv_bfloat16* __restrict__ gate = nullptr, long long gate_stride = 0) {
+                   const __nv_bfloat16* __restrict__ gate = nullptr, long long gate_stride = 0, int keep = 0) {
+    // keep > 0 (with a window): the first `keep` tokens of a sequence stay visible behind the window
     // mask_chunk > 0: a query also sees only keys of its own block of mask_chunk positions (counted from
     // position 0); sinks: exp(sink[head]) joins the softmax's denominator (counted by the first split);
     // gate: the output of (token, head) is multiplied by sigmoid(gate[token * gate_stride + head])
@@ -92,14 +93,21 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
     const int p_max = base_pos + last_row / n_rep;
+    const int chunk_lo = mask_chunk > 0 ? (p_min / mask_chunk) * mask_chunk : 0;
     int key_lo = window > 0 ? max(0, p_min - window + 1) : 0;
-    if (mask_chunk > 0) key_lo = max(key_lo, (p_min / mask_chunk) * mask_chunk);
+    key_lo = max(key_lo, chunk_lo);
     const int kt_lo = key_lo / FA_BK, kt_hi = p_max / FA_BK;
-    const int ntiles_all = kt_hi - kt_lo + 1;
+    // kept first tokens that the window has left behind: their tiles come before the window's
+    const int keep_hi = (window > 0 && keep > 0) ? min(keep, key_lo) : 0;
+    const int kf_lo = chunk_lo / FA_BK;
+    const int n_first = keep_hi > chunk_lo ? max(0, min((keep_hi + FA_BK - 1) / FA_BK, kt_lo) - kf_lo) : 0;
+    const int ntiles_all = n_first + kt_hi - kt_lo + 1;
     const int chunk = (ntiles_all + splits - 1) / splits;
-    const int kt_begin = kt_lo + sp * chunk;
-    const int kt_end = min(kt_hi + 1, kt_begin + chunk);
-    const int nt = max(0, kt_end - kt_begin);
+    const int it_begin = sp * chunk;
+    const int it_end = min(ntiles_all, it_begin + chunk);
+    const int nt = max(0, it_end - it_begin);
+    // the it-th tile of this block's walk
+    auto tile_of = [&](int it) { const int a = it_begin + it; return a < n_first ? kf_lo + a : kt_lo + (a - n_first); };
 
     // this thread's two rows: (gq) and (gq + 8) of the warp's 16
     int row_id[2], row_pos[2], row_tok[2], row_head[2], row_lo[2];
@@ -133,7 +141,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         int page = bt[k0 / page_size];
         bool page_ok = page >= 0 && page < num_pages;
         if (!page_ok) {
-            if (threadIdx.x == 0 && status && k0 <= key_hi && k0 + FA_BK > key_lo) atomicExch(status, 4);
+            if (threadIdx.x == 0 && status && k0 <= key_hi && (k0 + FA_BK > key_lo || k0 < keep_hi)) atomicExch(status, 4);
             page = 0;
         }
         const __nv_bfloat16* kbase = cache + ((((size_t)page * 2) * nkv + g) * page_size + (k0 % page_size)) * HD;
@@ -143,7 +151,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         for (int i = threadIdx.x; i < FA_BK * CPR; i += NWARPS * 32) {
             const int r = i / CPR, c = i - r * CPR;
             const int kj = k0 + r;
-            const int bytes = (page_ok && kj >= key_lo && kj <= key_hi) ? 16 : 0;   // 0: zero-fill
+            const int bytes = (page_ok && (kj >= key_lo || (kj < keep_hi && kj >= chunk_lo)) && kj <= key_hi) ? 16 : 0;   // 0: zero-fill
             const int doff = r * HD + ((c ^ (r & 7)) << 3);
             cp_async_16(dk + doff, kbase + r * HD + c * 8, bytes);
             cp_async_16(dv + doff, vbase + r * HD + c * 8, bytes);
@@ -153,11 +161,12 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     // Tiles that hold only keys of earlier steps do not depend on the kernel before this one
     // (which wrote this step's keys and rotated this step's queries): bring them in first.
     const int kt_old_end = base_pos / FA_BK;
-    const int pre = max(0, min(min(STAGES - 1, nt), kt_old_end - kt_begin));
+    int pre = 0;
+    while (pre < min(STAGES - 1, nt) && tile_of(pre) < kt_old_end) ++pre;
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
         if (st < pre) {
-            load_tile(kt_begin + st, st);
+            load_tile(tile_of(st), st);
             cp_async_commit();
         }
     }
@@ -165,7 +174,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
         if (st >= pre) {
-            if (st < nt) load_tile(kt_begin + st, st);
+            if (st < nt) load_tile(tile_of(st), st);
             cp_async_commit();
         }
     }
@@ -191,13 +200,13 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     for (int it = 0; it < nt; ++it) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();
-        if (it + STAGES - 1 < nt) load_tile(kt_begin + it + STAGES - 1, (it + STAGES - 1) % STAGES);
+        if (it + STAGES - 1 < nt) load_tile(tile_of(it + STAGES - 1), (it + STAGES - 1) % STAGES);
         cp_async_commit();
 
-        const int kt = kt_begin + it;
+        const int kt = tile_of(it);
         const int k0 = kt * FA_BK;
         // a warp none of whose rows reaches this tile (causal) or whose window has passed it skips it
-        if (!warp_has_rows || k0 > w_pos_max || (window > 0 && k0 + FA_BK - 1 <= w_pos_min - window) ||
+        if (!warp_has_rows || k0 > w_pos_max || (window > 0 && k0 + FA_BK - 1 <= w_pos_min - window && k0 >= keep) ||
             (mask_chunk > 0 && k0 + FA_BK - 1 < (w_pos_min / mask_chunk) * mask_chunk)) continue;
         const __nv_bfloat16* ks = sK + (it % STAGES) * TILE;
         const __nv_bfloat16* vs = sV + (it % STAGES) * TILE;
@@ -232,7 +241,7 @@ flash_paged_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                     float v = sc[i][2 * h + e] * scale_log2e;
                     if (need_mask) {
                         const int kj = k0 + i * 8 + 2 * tq + e;
-                        const bool vis = kj <= row_pos[h] && kj < klen && (window <= 0 || kj > row_pos[h] - window) &&
+                        const bool vis = kj <= row_pos[h] && kj < klen && (window <= 0 || kj > row_pos[h] - window || kj < keep) &&
                                          kj >= row_lo[h];
                         v = vis ? v : -INFINITY;
                     }
@@ -328,7 +337,8 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
                         const int* seqlens_k, void* out, float* part_o, float* part_ml, int num_seqs,
                         int max_q, int nh, int nkv, int page_size, int num_pages, float scale,
                         int window, int splits, int* status, cudaStream_t stream, int q_below = 0, int rows_above = 0,
-                        int mask_chunk = 0, const float* sinks = nullptr, const void* gate = nullptr, long long gate_stride = 0) {
+                        int mask_chunk = 0, const float* sinks = nullptr, const void* gate = nullptr, long long gate_stride = 0,
+                        int keep = 0) {
     const int n_rep = nh / nkv;
     const long long max_rows = (long long)max_q * n_rep;
     const long long tiles = (max_rows + NWARPS * 16 - 1) / (NWARPS * 16);
@@ -346,7 +356,7 @@ static int launch_flash(const void* q, long long q_row_stride, const void* cache
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)cache, block_table, table_stride, cu_q,
         seqlens_k, (__nv_bfloat16*)out, part_o, part_ml, nh, nkv, page_size, num_pages,
         scale * 1.4426950408889634f, window, splits, q_below, rows_above, status, mask_chunk, sinks,
-        (const __nv_bfloat16*)gate, gate_stride));
+        (const __nv_bfloat16*)gate, gate_stride, keep));
 }
 
 }  // namespace vapi

@@ -58,6 +58,7 @@ struct FaTcParams {
     // joins the softmax's denominator; gate: the output of (token, head) is multiplied by
     // sigmoid(gate[token * gate_stride + head])
     int mask_chunk;
+    int keep;                  // with a window: the first `keep` tokens of a sequence stay visible behind it
     const float* sinks;
     const __nv_bfloat16* gate;
     long long gate_stride;
@@ -96,10 +97,16 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
     const int base_pos = klen - qlen;
     const int p_min = base_pos + tile_start / n_rep;
     const int p_max = base_pos + last_row / n_rep;
+    const int chunk_lo = p.mask_chunk > 0 ? (p_min / p.mask_chunk) * p.mask_chunk : 0;
     int key_lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
-    if (p.mask_chunk > 0) key_lo = max(key_lo, (p_min / p.mask_chunk) * p.mask_chunk);
+    key_lo = max(key_lo, chunk_lo);
     const int kt_lo = key_lo / FT_BK, kt_hi = p_max / FT_BK;
-    const int nt = kt_hi - kt_lo + 1;
+    // kept first tokens that the window has left behind: their tiles come before the window's
+    const int keep_hi = (p.window > 0 && p.keep > 0) ? min(p.keep, key_lo) : 0;
+    const int kf_lo = chunk_lo / FT_BK;
+    const int n_first = keep_hi > chunk_lo ? max(0, min((keep_hi + FT_BK - 1) / FT_BK, kt_lo) - kf_lo) : 0;
+    const int nt = n_first + kt_hi - kt_lo + 1;
+    auto tile_of = [&](int i) { return i < n_first ? kf_lo + i : kt_lo + (i - n_first); };
 
     const unsigned kv_full = smem_u32(bars), kv_empty = smem_u32(bars + FT_STAGES);
     const unsigned s_full = smem_u32(bars + 2 * FT_STAGES), s_free = smem_u32(bars + 2 * FT_STAGES + 2);
@@ -135,7 +142,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
             bool waited = false;
             for (int i = 0; i < nt; ++i) {
                 const int stage = i % FT_STAGES;
-                const int k0 = (kt_lo + i) * FT_BK;
+                const int k0 = tile_of(i) * FT_BK;
                 if (i >= FT_STAGES && !mbar_wait(kv_empty + 8 * stage, ((i / FT_STAGES) - 1) & 1)) { flags[0] = 1; break; }
                 // a tile that reaches into this step's keys was written by the kernel before this one
                 if (!waited && k0 + FT_BK > base_pos) { pdl_wait(); waited = true; }
@@ -217,7 +224,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
         bool ok = true;
         for (int i = 0; i < nt && ok; ++i) {
             const int sb = i & 1, stage = i % FT_STAGES;
-            const int k0 = (kt_lo + i) * FT_BK;
+            const int k0 = tile_of(i) * FT_BK;
             // (a wait's outcome is made uniform over the warp: the tensor-memory accesses below are
             // warp-wide instructions)
             if (!__all_sync(0xffffffffu, mbar_wait(s_full + 8 * sb, (i >> 1) & 1))) { ok = false; break; }
@@ -246,7 +253,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tm_kv, const FaTcParams p) {
 #pragma unroll
                 for (int e = 0; e < FT_BK; ++e) {
                     const int kj = k0 + e;
-                    const bool vis = kj <= pos && kj < klen && (p.window <= 0 || kj > pos - p.window) && kj >= pos_lo;
+                    const bool vis = kj <= pos && kj < klen && (p.window <= 0 || kj > pos - p.window || kj < p.keep) && kj >= pos_lo;
                     sv[e] = vis ? sv[e] : -INFINITY;
                     mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
                 }
@@ -362,7 +369,7 @@ static int launch_flash_tc(const void* q, long long q_row_stride, const void* ca
                            int table_stride, const int* cu_q, const int* seqlens_k, void* out, int num_seqs,
                            int max_q, int nh, int nkv, int page_size, int num_pages, float scale, int window,
                            int min_q, int* status, cudaStream_t stream, int mask_chunk = 0, const float* sinks = nullptr,
-                           const void* gate = nullptr, long long gate_stride = 0) {
+                           const void* gate = nullptr, long long gate_stride = 0, int keep = 0) {
     const int n_rep = nh / nkv;
     const long long tiles = ((long long)max_q * n_rep + FT_ROWS - 1) / FT_ROWS;
     if (tiles > 0x7fffffffLL || nkv > 65535 || num_seqs > 65535)
@@ -383,7 +390,7 @@ static int launch_flash_tc(const void* q, long long q_row_stride, const void* ca
     p.q = (const __nv_bfloat16*)q; p.q_row_stride = q_row_stride; p.block_table = block_table; p.table_stride = table_stride;
     p.cu_q = cu_q; p.seqlens_k = seqlens_k; p.out = (__nv_bfloat16*)out; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
     p.num_pages = num_pages; p.scale_log2e = scale * 1.4426950408889634f; p.window = window; p.min_q = min_q; p.status = status;
-    p.mask_chunk = mask_chunk; p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.mask_chunk = mask_chunk; p.keep = keep; p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
     dim3 grid((unsigned)tiles, nkv, num_seqs);
     return check_launch("paged_attention (tcgen05)", launch(flash_tc_kernel, grid, FT_THREADS, FT_SMEM, stream, map, p));
 }

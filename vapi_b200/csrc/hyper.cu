@@ -1,0 +1,277 @@
+// Several residual streams side by side (hyper-connections), the layer norm that reads them, and the
+// small elementwise steps of mixers that run side by side.
+//
+// The residual state of a token is S copies of a row, x[t, s, :] (float).  A sublayer reads
+// u = sum_s read[s] x_s through a norm, and writes its output y back as
+//     x_t <- sum_s mix[s, t] x_s + write[t] y          (all copies at once, from the old ones).
+// As with a single stream, a sublayer's output is not written by a pass of its own: it is handed on,
+// and the kernel that reads the streams for the next sublayer first applies the pending write, then
+// forms u and norms it, one block a token.  S = 1 with mix = write = read = 1 is the ordinary
+// residual sum, so the same kernel serves a model with one stream.
+//
+// Norms: kind 0 is a layer norm with a weight and no bias, (u - mean) / sqrt(var + eps) * w with the
+// variance taken as the mean of the squared deviations (two passes over the row, which is kept in
+// shared memory); kind 1 is an RMS norm, u / sqrt(mean u^2 + eps) * w.  Sums are float.
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int HC_MAX_STREAMS = 8;
+
+// x[t, s, c] = table[token[t], c] + (c even ? sin : cos)(position[t] * freq[c / 2]) for every copy s.
+// freq is float, rounded once from the exact value; the angle is one float product.
+template <typename T>
+__global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                                      const int* __restrict__ positions, const float* __restrict__ freq,
+                                      float* __restrict__ x, int n, int hidden, int vocab, int streams,
+                                      int* __restrict__ status) {
+    const int t = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (t >= n) return;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 1);
+        tok = 0;
+    }
+    const float p = (float)positions[t];
+    const T* row = table + (size_t)tok * hidden;
+    float* xr = x + (size_t)t * streams * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = to_f32(row[c]);
+        if (freq) {
+            const float angle = p * freq[c >> 1];
+            v += (c & 1) ? cosf(angle) : sinf(angle);
+        }
+        for (int s = 0; s < streams; ++s) xr[(size_t)s * hidden + c] = v;
+    }
+}
+
+VAPI_EXPORT int vapi_embed_sinusoid(const void* table, int dtype, const int* tokens, const int* positions,
+                                    const float* freq, float* x, int n, int hidden, int vocab, int streams, int* status,
+                                    cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0 || streams < 1 || streams > HC_MAX_STREAMS)
+        return fail(-1, "embed_sinusoid: hidden=%d vocab=%d streams=%d", hidden, vocab, streams);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(embed_sinusoid_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, positions, freq, x, n,
+                   hidden, vocab, streams, status);
+    else if (dtype == VAPI_BF16)
+        e = launch(embed_sinusoid_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, positions,
+                   freq, x, n, hidden, vocab, streams, status);
+    else
+        return fail(-2, "embed_sinusoid: unsupported dtype %d", dtype);
+    return check_launch("embed_sinusoid", e);
+}
+
+// One block a wanted row.  y (may be null: nothing pending), mix [S, S] indexed [from, to], write [S],
+// read [S] (null: every copy counts once).  With `rows` the streams are left as they are (the pending
+// write is applied on the fly).  w null: only the streams are updated.
+template <typename T>
+__global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mix,
+                                       const float* __restrict__ write, const float* __restrict__ read,
+                                       const float* __restrict__ w, float eps, int kind, const int* __restrict__ rows,
+                                       T* __restrict__ out, int n_out, int hidden, int streams, int write_x) {
+    extern __shared__ float hc_row[];          // the row u, [hidden]
+    __shared__ float red[33];
+    __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_write[HC_MAX_STREAMS], s_read[HC_MAX_STREAMS];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    if (threadIdx.x < streams * streams) s_mix[threadIdx.x] = (y && mix) ? mix[threadIdx.x] : 0.f;
+    if (threadIdx.x < streams) {
+        s_write[threadIdx.x] = (y && write) ? write[threadIdx.x] : 0.f;
+        s_read[threadIdx.x] = read ? read[threadIdx.x] : 1.f;
+    }
+    pdl_wait();
+    if (j >= n_out) return;
+    __syncthreads();
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * streams * hidden;
+    const T* yr = y ? y + (size_t)row * hidden : nullptr;
+    float sum = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float old[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s) old[s] = s < streams ? xr[(size_t)s * hidden + c] : 0.f;
+        float u = 0.f;
+        if (yr) {
+            const float yv = to_f32(yr[c]);
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t) {
+                if (t < streams) {
+                    float v = s_write[t] * yv;
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                        if (s < streams) v = fmaf(s_mix[s * streams + t], old[s], v);
+                    if (write_x) xr[(size_t)t * hidden + c] = v;
+                    u = fmaf(s_read[t], v, u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < streams) u = fmaf(s_read[t], old[t], u);
+        }
+        hc_row[c] = u;
+        sum += kind == 0 ? u : u * u;
+    }
+    if (!w) return;
+    sum = block_sum(sum, red);
+    float mean = 0.f, inv;
+    if (kind == 0) {
+        mean = sum / (float)hidden;
+        float dev = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float d = hc_row[c] - mean;      // each thread reads back what it wrote itself
+            dev += d * d;
+        }
+        dev = block_sum(dev, red);
+        inv = rsqrtf(dev / (float)hidden + eps);
+    } else {
+        inv = rsqrtf(sum / (float)hidden + eps);
+    }
+    T* orow = out + (size_t)j * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) orow[c] = from_f32<T>((hc_row[c] - mean) * inv * w[c]);
+}
+
+VAPI_EXPORT int vapi_hyper_read_norm(float* x, const void* y, int dtype, const float* mix, const float* write,
+                                     const float* read, const float* w, float eps, int kind, const int* rows, void* out,
+                                     int n_out, int hidden, int streams, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (hidden <= 0 || streams < 1 || streams > HC_MAX_STREAMS)
+        return fail(-1, "hyper_read_norm: hidden=%d streams=%d (at most %d)", hidden, streams, HC_MAX_STREAMS);
+    if (y && (!mix || !write)) return fail(-1, "hyper_read_norm: a pending output needs its mix matrix and write vector");
+    if (w && !out) return fail(-1, "hyper_read_norm: a norm needs an output");
+    if (kind != 0 && kind != 1) return fail(-1, "hyper_read_norm: norm kind %d", kind);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return fail(-1, "hyper_read_norm: rows of %d do not fit shared memory", hidden);
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const int write_x = rows ? 0 : 1;
+    cudaError_t e;
+    if (dtype == VAPI_F32) {
+        auto kern = hyper_read_norm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = launch(kern, n_out, threads, smem, stream, x, (const float*)y, mix, write, read, w, eps, kind, rows, (float*)out,
+                   n_out, hidden, streams, write_x);
+    } else if (dtype == VAPI_BF16) {
+        auto kern = hyper_read_norm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = launch(kern, n_out, threads, smem, stream, x, (const __nv_bfloat16*)y, mix, write, read, w, eps, kind, rows,
+                   (__nv_bfloat16*)out, n_out, hidden, streams, write_x);
+    } else {
+        return fail(-2, "hyper_read_norm: unsupported dtype %d", dtype);
+    }
+    return check_launch("hyper_read_norm", e);
+}
+
+// out[t, :] = scale * sum_b rmsnorm(a_b[t, :]) * w_b  for up to four branches: what mixers that run side by
+// side on one input leave.  One block a row; the branch rows are read twice (the second time from cache).
+constexpr int BR_MAX = 4;
+template <typename T>
+struct BranchPtrs {
+    const T* a[BR_MAX];
+    const float* w[BR_MAX];
+};
+
+template <typename T>
+__global__ void branch_rmsnorm_mean_kernel(BranchPtrs<T> p, int branches, float eps, float scale, T* __restrict__ out, int n,
+                                           int hidden) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (t >= n) return;
+    float inv[BR_MAX];
+#pragma unroll
+    for (int b = 0; b < BR_MAX; ++b) {
+        inv[b] = 0.f;
+        if (b < branches) {
+            const T* r = p.a[b] + (size_t)t * hidden;
+            float ss = 0.f;
+            for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+                const float v = to_f32(r[c]);
+                ss += v * v;
+            }
+            ss = block_sum(ss, red);
+            inv[b] = rsqrtf(ss / (float)hidden + eps);
+        }
+    }
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int b = 0; b < BR_MAX; ++b)
+            if (b < branches) acc += to_f32(p.a[b][(size_t)t * hidden + c]) * inv[b] * p.w[b][c];
+        out[(size_t)t * hidden + c] = from_f32<T>(acc * scale);
+    }
+}
+
+VAPI_EXPORT int vapi_branch_rmsnorm_mean(const void* const* a, const float* const* w, int branches, int dtype, float eps,
+                                         float scale, void* out, int n, int hidden, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (branches < 1 || branches > BR_MAX || hidden <= 0)
+        return fail(-1, "branch_rmsnorm_mean: %d branches (at most %d), hidden=%d", branches, BR_MAX, hidden);
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaError_t e;
+    if (dtype == VAPI_F32) {
+        BranchPtrs<float> p = {};
+        for (int b = 0; b < branches; ++b) { p.a[b] = (const float*)a[b]; p.w[b] = w[b]; }
+        e = launch(branch_rmsnorm_mean_kernel<float>, n, threads, 0, stream, p, branches, eps, scale, (float*)out, n, hidden);
+    } else if (dtype == VAPI_BF16) {
+        BranchPtrs<__nv_bfloat16> p = {};
+        for (int b = 0; b < branches; ++b) { p.a[b] = (const __nv_bfloat16*)a[b]; p.w[b] = w[b]; }
+        e = launch(branch_rmsnorm_mean_kernel<__nv_bfloat16>, n, threads, 0, stream, p, branches, eps, scale,
+                   (__nv_bfloat16*)out, n, hidden);
+    } else {
+        return fail(-2, "branch_rmsnorm_mean: unsupported dtype %d", dtype);
+    }
+    return check_launch("branch_rmsnorm_mean", e);
+}
+
+// out[t, c] = y[t, c] * sigmoid(g[t * g_stride + c]): a gate as wide as what it multiplies.
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ y, const T* __restrict__ g, long long g_stride,
+                                    T* __restrict__ out, long long total, int width) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= total) return;
+    const long long t = i / width;
+    const int c = (int)(i - t * width);
+    const float gv = to_f32(g[(size_t)t * g_stride + c]);
+    out[i] = from_f32<T>(to_f32(y[i]) * (1.f / (1.f + expf(-gv))));
+}
+
+VAPI_EXPORT int vapi_sigmoid_gate(const void* y, const void* g, long long g_stride, int dtype, void* out, int n, int width,
+                                  cudaStream_t stream) {
+    if (n <= 0 || width <= 0) return 0;
+    const long long total = (long long)n * width;
+    const int blocks = (int)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (const float*)y, (const float*)g, g_stride, (float*)out,
+                   total, width);
+    else if (dtype == VAPI_BF16)
+        e = launch(sigmoid_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)y, (const __nv_bfloat16*)g,
+                   g_stride, (__nv_bfloat16*)out, total, width);
+    else
+        return fail(-2, "sigmoid_gate: unsupported dtype %d", dtype);
+    return check_launch("sigmoid_gate", e);
+}
+
+// x <- cap * tanh(x / cap) in place (float logits).
+__global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i < total) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+VAPI_EXPORT int vapi_softcap(float* x, float cap, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return fail(-1, "softcap: the cap must be positive");
+    return check_launch("softcap", launch(softcap_kernel, (int)((total + 255) / 256), 256, 0, stream, x, cap, 1.f / cap, total));
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

@@ -1,0 +1,346 @@
+// A mixture of small feed-forward experts: the router, the plan of a step's expert work, the experts'
+// two matrix products over tokens grouped by expert, and the weighted sum.
+//
+// Router (float whatever the activation type): z = Wr h over all `outputs` = experts + identity
+// experts; s = softmax(z); the choice score is s + correction; outputs form `groups` equal groups of
+// neighbours, a group's score is its largest choice score, and only outputs of the `keep` best groups
+// can be chosen (the others count as minus infinity); the `top` largest choice scores win (ties: the
+// lower index); their weights are their s divided by the sum of the chosen s (+ 1e-20).  An output
+// index >= experts is an identity expert: its output is the input itself.
+//
+// The step's expert work is laid out without the host learning anything about it: the router counts
+// the tokens of each expert and gives every (token, choice) pair its rank within its expert; one block
+// then turns the counts into offsets, lists the pairs expert by expert and cuts each expert's list into
+// tiles of 64 rows.  The two products launch enough blocks for the worst case; a block whose tile does
+// not exist returns at once.  up: hid[pos] = relu(W_up[e] h[token])^2; down: y[pair] = weight *
+// W_down[e] hid[pos] in float; the sum over a token's pairs, its identity experts and the shared expert
+// is taken in a fixed order.
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
+
+// One warp per token.  shared memory: per warp 2 * outputs floats (s and the choice scores) + groups floats.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
+                                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ ranks,
+                                 int* __restrict__ counts, int n, int width, int outputs, int experts, int top, int groups,
+                                 int keep) {
+    extern __shared__ float rt_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    float* s = rt_smem + (size_t)warp * (2 * outputs + groups);
+    float* choice = s + outputs;
+    float* gscore = choice + outputs;
+    pdl_trigger();
+    pdl_wait();
+    if (t >= n) return;
+    const T* hr = h + (size_t)t * width;
+    for (int e = 0; e < outputs; ++e) {
+        const float* w = wr + (size_t)e * width;
+        float acc = 0.f;
+        for (int k = lane; k < width; k += 32) acc = fmaf(to_f32(hr[k]), w[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) s[e] = acc;
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) sum += expf(s[e] - mx);
+    sum = warp_sum(sum);
+    for (int e = lane; e < outputs; e += 32) {
+        const float p = expf(s[e] - mx) / sum;
+        s[e] = p;
+        choice[e] = p + corr[e];
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int per = outputs / groups;
+        for (int gi = lane; gi < groups; gi += 32) {
+            float m = -INFINITY;
+            for (int e = gi * per; e < (gi + 1) * per; ++e) m = fmaxf(m, choice[e]);
+            gscore[gi] = m;
+        }
+        __syncwarp();
+        // the best `keep` groups, one after the other; a chosen group is marked by +inf
+        for (int r = 0; r < keep; ++r) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int gi = lane; gi < groups; gi += 32) {
+                const float v = gscore[gi];
+                if (v != INFINITY && (v > bv || (v == bv && gi < bi) || bi == 0x7fffffff)) { bv = v; bi = gi; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            }
+            if (lane == 0 && bi != 0x7fffffff) gscore[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < outputs; e += 32)
+            if (gscore[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
+    float total = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32) {
+            const float v = choice[e];
+            if (!isnan(v) && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;              // (cannot happen with top <= the outputs that may be chosen)
+        const float p = s[bi];
+        total += p;
+        if (lane == 0) {
+            ids[(size_t)t * top + r] = bi;
+            wts[(size_t)t * top + r] = p;
+            ranks[(size_t)t * top + r] = bi < experts ? atomicAdd(counts + bi, 1) : -1;
+            choice[bi] = NAN;                      // taken
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float inv = 1.f / (total + 1e-20f);
+        for (int r = 0; r < top; ++r) wts[(size_t)t * top + r] *= inv;
+    }
+}
+
+// One block: counts -> offsets; the pairs expert by expert; the tiles.  plan[0] = number of tiles.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, const int* __restrict__ ranks, const int* __restrict__ counts,
+                                int* __restrict__ offsets, int* __restrict__ pair_of, int* __restrict__ plan,
+                                int* __restrict__ tile_expert, int* __restrict__ tile_row0, int pairs, int experts) {
+    extern __shared__ int pl_off[];            // [experts + 1]
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int acc = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            pl_off[e] = acc;
+            offsets[e] = acc;
+            const int c = counts[e];
+            for (int r = 0; r < c; r += MOE_TM) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = acc + r;
+                ++tiles;
+            }
+            acc += c;
+        }
+        pl_off[experts] = acc;
+        offsets[experts] = acc;
+        plan[0] = tiles;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e < experts) pair_of[pl_off[e] + ranks[p]] = p;
+    }
+}
+
+// out rows of one tile = act(A rows x W[e]^T): A [*, K] rows gathered through `src` (pair / src_div when
+// gather, else the sorted position itself), W [experts, N, K].  MODE 0 (up): out[pos, :] = relu(.)^2 in T.
+// MODE 1 (down): out[pair, :] = weight[pair] * (.) in float.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restrict__ W, const int* __restrict__ plan,
+                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                   const int* __restrict__ offsets, const int* __restrict__ pair_of, const float* __restrict__ wts,
+                   void* __restrict__ out, int N, int K, int top) {
+    __shared__ float As[MOE_TK][MOE_TM + 4];
+    __shared__ float Ws[MOE_TK][MOE_TN + 4];
+    __shared__ int s_src[MOE_TM], s_dst[MOE_TM];
+    const int tile = blockIdx.x;
+    const int c0 = blockIdx.y * MOE_TN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    pdl_trigger();
+    pdl_wait();
+    if (tile >= plan[0]) return;
+    const int e = tile_expert[tile], row0 = tile_row0[tile];
+    const int rows = min(MOE_TM, offsets[e + 1] - row0);
+    if (threadIdx.x < MOE_TM) {
+        int src = -1, dst = -1;
+        if ((int)threadIdx.x < rows) {
+            const int pos = row0 + threadIdx.x;
+            const int pair = pair_of[pos];
+            src = MODE == 0 ? pair / top : pos;
+            dst = MODE == 0 ? pos : pair;
+        }
+        s_src[threadIdx.x] = src;
+        s_dst[threadIdx.x] = dst;
+    }
+    __syncthreads();
+    const T* We = W + (size_t)e * N * K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+        for (int idx = threadIdx.x; idx < MOE_TM * MOE_TK; idx += 256) {
+            const int rr = idx / MOE_TK, kk = idx - rr * MOE_TK;
+            const int src = s_src[rr], k = k0 + kk;
+            As[kk][rr] = (src >= 0 && k < K) ? to_f32(A[(size_t)src * a_stride + k]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < MOE_TN * MOE_TK; idx += 256) {
+            const int cc = idx / MOE_TK, kk = idx - cc * MOE_TK;
+            const int c = c0 + cc, k = k0 + kk;
+            Ws[kk][cc] = (c < N && k < K) ? to_f32(We[(size_t)c * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_TK; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 wv = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+            const float aa[4] = {av.x, av.y, av.z, av.w};
+            const float ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], ww[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int dst = s_dst[ty * 4 + i];
+        if (dst < 0) continue;
+        const float g = MODE == 1 ? wts[dst] : 1.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + tx * 4 + j;
+            if (c >= N) continue;
+            if (MODE == 0) {
+                const float r = fmaxf(acc[i][j], 0.f);
+                reinterpret_cast<T*>(out)[(size_t)dst * N + c] = from_f32<T>(r * r);
+            } else {
+                reinterpret_cast<float*>(out)[(size_t)dst * N + c] = g * acc[i][j];
+            }
+        }
+    }
+}
+
+// out[t, :] = sum over the token's choices (an expert's row of y, or weight * h for an identity expert)
+// + shared[t, :] (when given), in the order of the choices.
+template <typename T>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ ids, const float* __restrict__ wts,
+                                   const T* __restrict__ h, const T* __restrict__ shared, T* __restrict__ out, int n,
+                                   int width, int top, int experts) {
+    const int t = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (t >= n) return;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < top; ++r) {
+            const size_t p = (size_t)t * top + r;
+            acc += ids[p] < experts ? y[p * width + c] : wts[p] * to_f32(h[(size_t)t * width + c]);
+        }
+        if (shared) acc += to_f32(shared[(size_t)t * width + c]);
+        out[(size_t)t * width + c] = from_f32<T>(acc);
+    }
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ out, long long total) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= total) return;
+    const float r = fmaxf(to_f32(x[i]), 0.f);
+    out[i] = from_f32<T>(r * r);
+}
+
+VAPI_EXPORT int vapi_relu_squared(const void* x, void* out, int dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == VAPI_F32) e = launch(relu_squared_kernel<float>, blocks, 256, 0, stream, (const float*)x, (float*)out, total);
+    else if (dtype == VAPI_BF16)
+        e = launch(relu_squared_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, total);
+    else return fail(-2, "relu_squared: unsupported dtype %d", dtype);
+    return check_launch("relu_squared", e);
+}
+
+// ids, wts, ranks: [n, top]; counts: [experts] (cleared here); offsets: [experts + 1]; pair_of: [n * top];
+// plan: [1]; tile_expert, tile_row0: [max_tiles] with max_tiles >= n * top / 64 + experts.
+VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const float* corr, int* ids, float* wts, int* ranks,
+                               int* counts, int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
+                               int width, int outputs, int experts, int top, int groups, int keep, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (outputs <= 0 || experts < 0 || experts > outputs || top <= 0 || top > outputs)
+        return fail(-1, "moe_route: %d outputs, %d experts, top %d", outputs, experts, top);
+    if (groups < 1 || outputs % groups || keep < 1 || keep > groups)
+        return fail(-1, "moe_route: %d outputs in %d groups, %d kept", outputs, groups, keep);
+    if ((long long)(outputs / groups) * keep < top) return fail(-1, "moe_route: %d kept groups cannot give %d choices", keep, top);
+    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(experts > 0 ? experts : 1), stream);
+    if (e != cudaSuccess) return fail(-100, "moe_route: memset failed: %s", cudaGetErrorString(e));
+    const int warps = 4;
+    const size_t smem = (size_t)warps * (2 * outputs + groups) * sizeof(float);
+    if (smem > 48 * 1024) return fail(-1, "moe_route: %d router outputs are too many", outputs);
+    const int blocks = (n + warps - 1) / warps;
+    if (dtype == VAPI_F32)
+        e = launch(moe_route_kernel<float>, blocks, warps * 32, smem, stream, (const float*)h, wr, corr, ids, wts, ranks, counts,
+                   n, width, outputs, experts, top, groups, keep);
+    else if (dtype == VAPI_BF16)
+        e = launch(moe_route_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream, (const __nv_bfloat16*)h, wr, corr, ids, wts,
+                   ranks, counts, n, width, outputs, experts, top, groups, keep);
+    else
+        return fail(-2, "moe_route: unsupported dtype %d", dtype);
+    int rc = check_launch("moe_route", e);
+    if (rc != 0 || experts == 0) return rc;
+    const size_t psm = sizeof(int) * (size_t)(experts + 1);
+    if (psm > 48 * 1024) return fail(-1, "moe_route: %d experts are too many", experts);
+    e = launch(moe_plan_kernel, 1, 1024, psm, stream, (const int*)ids, (const int*)ranks, (const int*)counts, offsets, pair_of,
+               plan, tile_expert, tile_row0, n * top, experts);
+    return check_launch("moe_plan", e);
+}
+
+// mode 0: out = hid [n * top, N] in the activation type from A = h [n, K]; mode 1: out = y [n * top, N] float
+// from A = hid [n * top, K].
+VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* W, int dtype, const int* plan,
+                                 const int* tile_expert, const int* tile_row0, const int* offsets, const int* pair_of,
+                                 const float* wts, void* out, int pairs, int experts, int N, int K, int top, int mode,
+                                 cudaStream_t stream) {
+    if (pairs <= 0 || experts <= 0) return 0;
+    const int max_tiles = pairs / MOE_TM + experts;
+    dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
+    if (grid.y > 65535) return fail(-1, "moe_grouped: %d output features are too many", N);
+    cudaError_t e;
+#define MOE_GO(T, M)                                                                                                         \
+    e = launch(moe_grouped_kernel<T, M>, grid, 256, 0, stream, (const T*)A, a_stride, (const T*)W, plan, tile_expert,         \
+               tile_row0, offsets, pair_of, wts, out, N, K, top)
+    if (dtype == VAPI_F32) { if (mode == 0) MOE_GO(float, 0); else MOE_GO(float, 1); }
+    else if (dtype == VAPI_BF16) { if (mode == 0) MOE_GO(__nv_bfloat16, 0); else MOE_GO(__nv_bfloat16, 1); }
+    else return fail(-2, "moe_grouped: unsupported dtype %d", dtype);
+#undef MOE_GO
+    return check_launch("moe_grouped", e);
+}
+
+VAPI_EXPORT int vapi_moe_combine(const float* y, const int* ids, const float* wts, const void* h, const void* shared,
+                                 void* out, int dtype, int n, int width, int top, int experts, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    cudaError_t e;
+    if (dtype == VAPI_F32)
+        e = launch(moe_combine_kernel<float>, n, threads, 0, stream, y, ids, wts, (const float*)h, (const float*)shared,
+                   (float*)out, n, width, top, experts);
+    else if (dtype == VAPI_BF16)
+        e = launch(moe_combine_kernel<__nv_bfloat16>, n, threads, 0, stream, y, ids, wts, (const __nv_bfloat16*)h,
+                   (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, n, width, top, experts);
+    else
+        return fail(-2, "moe_combine: unsupported dtype %d", dtype);
+    return check_launch("moe_combine", e);
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

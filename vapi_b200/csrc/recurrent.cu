@@ -31,7 +31,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long x_str
                                         long long slot_stride, const int* __restrict__ state_slots,
                                         const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
                                         const int* __restrict__ positions, T* __restrict__ out, int n, int num_seqs,
-                                        int channels, int L, int num_slots, int head_blocks, int* __restrict__ status) {
+                                        int channels, int L, int num_slots, int head_blocks, int* __restrict__ status, int act) {
     pdl_trigger();
     if ((int)blockIdx.x < head_blocks) {
         const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -70,7 +70,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long x_str
         for (int i = 0; i < head; ++i) {
             float acc = b;
             for (int j = 0; j < L; ++j) acc = fmaf(w[j], win[i + j], acc);
-            out[(size_t)(q0 + i) * channels + c] = from_f32<T>(silu_f(acc));
+            out[(size_t)(q0 + i) * channels + c] = from_f32<T>(act ? silu_f(acc) : acc);
         }
         // the new state: the last L-1 inputs before position start + qlen
         for (int r = 0; r < L - 1; ++r) {
@@ -92,7 +92,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long x_str
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < L; ++j)
         acc = fmaf(taps[(size_t)j * channels + c], to_f32(x[(size_t)(t - (L - 1) + j) * x_stride + c]), acc);
-    out[(size_t)t * channels + c] = from_f32<T>(silu_f(acc));
+    out[(size_t)t * channels + c] = from_f32<T>(act ? silu_f(acc) : acc);
 }
 
 // The (token, channel) part with 16-byte accesses: a thread takes VEC consecutive channels of one
@@ -134,7 +134,7 @@ template <> struct ConvVec<__nv_bfloat16> {
 template <typename T>
 __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ taps,
                                             const float* __restrict__ bias, const int* __restrict__ tok_seq,
-                                            const int* __restrict__ cu_q, T* __restrict__ out, int n, int channels, int L) {
+                                            const int* __restrict__ cu_q, T* __restrict__ out, int n, int channels, int L, int act) {
     constexpr int VEC = ConvVec<T>::N;
     const int cv = channels / VEC;
     const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -170,14 +170,15 @@ __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ x, long long x
         }
     }
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+    for (int e = 0; e < VEC; ++e) acc[e] = act ? silu_f(acc[e]) : acc[e];
     ConvVec<T>::store(out + (size_t)t * channels + c, acc);
 }
 
-VAPI_EXPORT int vapi_causal_conv_silu(const void* x, long long x_stride, int dtype, const float* taps, const float* bias,
-                                      float* state, long long slot_stride, const int* state_slots, const int* tok_seq,
-                                      const int* cu_q, const int* positions, void* out, int n, int num_seqs,
-                                      int channels, int L, int num_slots, int max_q, int* status, cudaStream_t stream) {
+// act 1: SiLU behind the convolution; act 0: the convolution's sum as it is.
+VAPI_EXPORT int vapi_causal_conv(const void* x, long long x_stride, int dtype, const float* taps, const float* bias,
+                                 float* state, long long slot_stride, const int* state_slots, const int* tok_seq,
+                                 const int* cu_q, const int* positions, void* out, int n, int num_seqs,
+                                 int channels, int L, int num_slots, int max_q, int act, int* status, cudaStream_t stream) {
     if (n <= 0 || num_seqs <= 0) return 0;
     if (channels <= 0 || L < 1 || L > CONV_MAX_L) return fail(-1, "causal_conv_silu: %d channels, %d taps", channels, L);
     if (L > 1 && !state) return fail(-1, "causal_conv_silu: a convolution of %d taps needs a state", L);
@@ -196,34 +197,42 @@ VAPI_EXPORT int vapi_causal_conv_silu(const void* x, long long x_stride, int dty
             if (dtype == VAPI_F32)
                 e = launch(causal_conv_silu_kernel<float>, head_blocks, threads, 0, stream, (const float*)x, x_stride, taps, bias, state,
                            slot_stride, state_slots, tok_seq, cu_q, positions, (float*)out, n, num_seqs, channels, L, num_slots,
-                           head_blocks, status);
+                           head_blocks, status, act);
             else
                 e = launch(causal_conv_silu_kernel<__nv_bfloat16>, head_blocks, threads, 0, stream, (const __nv_bfloat16*)x, x_stride,
                            taps, bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n, num_seqs,
-                           channels, L, num_slots, head_blocks, status);
+                           channels, L, num_slots, head_blocks, status, act);
             const int rc = check_launch("causal_conv_silu", e);
             if (rc != 0) return rc;
         }
         const int vblocks = (int)(((long long)n * (channels / vec) + threads - 1) / threads);
         if (dtype == VAPI_F32)
             e = launch(causal_conv_silu_vec_kernel<float>, vblocks, threads, 0, stream, (const float*)x, x_stride, taps, bias, tok_seq,
-                       cu_q, (float*)out, n, channels, L);
+                       cu_q, (float*)out, n, channels, L, act);
         else
             e = launch(causal_conv_silu_vec_kernel<__nv_bfloat16>, vblocks, threads, 0, stream, (const __nv_bfloat16*)x, x_stride, taps,
-                       bias, tok_seq, cu_q, (__nv_bfloat16*)out, n, channels, L);
+                       bias, tok_seq, cu_q, (__nv_bfloat16*)out, n, channels, L, act);
         return check_launch("causal_conv_silu", e);
     }
     if (dtype == VAPI_F32)
         e = launch(causal_conv_silu_kernel<float>, head_blocks + body_blocks, threads, 0, stream, (const float*)x, x_stride, taps,
                    bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, (float*)out, n, num_seqs, channels, L,
-                   num_slots, head_blocks, status);
+                   num_slots, head_blocks, status, act);
     else if (dtype == VAPI_BF16)
         e = launch(causal_conv_silu_kernel<__nv_bfloat16>, head_blocks + body_blocks, threads, 0, stream, (const __nv_bfloat16*)x,
                    x_stride, taps, bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, (__nv_bfloat16*)out, n,
-                   num_seqs, channels, L, num_slots, head_blocks, status);
+                   num_seqs, channels, L, num_slots, head_blocks, status, act);
     else
         return fail(-2, "causal_conv_silu: unsupported dtype %d", dtype);
     return check_launch("causal_conv_silu", e);
+}
+
+VAPI_EXPORT int vapi_causal_conv_silu(const void* x, long long x_stride, int dtype, const float* taps, const float* bias,
+                                      float* state, long long slot_stride, const int* state_slots, const int* tok_seq,
+                                      const int* cu_q, const int* positions, void* out, int n, int num_seqs,
+                                      int channels, int L, int num_slots, int max_q, int* status, cudaStream_t stream) {
+    return vapi_causal_conv(x, x_stride, dtype, taps, bias, state, slot_stride, state_slots, tok_seq, cu_q, positions, out, n,
+                            num_seqs, channels, L, num_slots, max_q, 1, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -80,11 +80,18 @@ class ModelRunner:
         #: enqueued before the host has read them takes its input tokens from here.
         self.sampled = self.status_and_sampled[1:]
         # one CacheView skeleton per run-order entry
-        self._site_of: List[Optional[int]] = []
+        # (a mixer that is several mixers side by side owns one site per member: (owner, member))
+        self._site_of: List[Any] = []
         for i, call in enumerate(plan.order):
             owner = call.cache_of if call.cache_of is not None else i
-            self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
-        self._site_buffers = {s: self.cache.site_buffers(s) for s in set(self._site_of) if s is not None}
+            spec = plan.layers[call.layer].mixer.cache_spec()
+            if isinstance(spec, tuple):
+                self._site_of.append([(owner, j) if self.cache.site_tensor((owner, j)) is not None else None
+                                      for j in range(len(spec))])
+            else:
+                self._site_of.append(owner if self.cache.site_tensor(owner) is not None else None)
+        flat = [s for e in self._site_of for s in (e if isinstance(e, list) else [e]) if s is not None]
+        self._site_buffers = {s: self.cache.site_buffers(s) for s in set(flat)}
         #: whether every block has the stream form that steps of few rows run (blocks without it hand
         #: their output on in another shape than a plain delta, so such a model takes the ordinary path)
         self._stream_form = all(hasattr(b, "forward_stream") for b in plan.layers)
@@ -146,18 +153,21 @@ class ModelRunner:
 
     # ---- the step ------------------------------------------------------------------
     def views(self, ctx: StepContext) -> List[CacheView]:
+        def one(site, write: bool) -> CacheView:
+            if site is None:
+                return CacheView("none")
+            kind, gi = self.cache.site_kind(site)
+            return CacheView(kind, self.cache.site_tensor(site), ctx.groups[gi] if kind == "paged" else None,
+                             write=write, buffers=self._site_buffers[site] if kind == "paged" else None,
+                             spec=self.cache.site_spec(site))
+
         out = []
         for i, call in enumerate(self.plan.order):
-            site = self._site_of[i]
-            if site is None:
-                out.append(CacheView("none"))
-                continue
-            kind, gi = self.cache.site_kind(site)
-            out.append(CacheView(kind, self.cache.site_tensor(site),
-                                 ctx.groups[gi] if kind == "paged" else None,
-                                 write=call.cache_of is None,
-                                 buffers=self._site_buffers[site] if kind == "paged" else None,
-                                 spec=self.cache.site_spec(site)))
+            site, write = self._site_of[i], call.cache_of is None
+            if isinstance(site, list):
+                out.append(CacheView("multi", write=write, parts=[one(s, write) for s in site]))
+            else:
+                out.append(one(site, write))
         return out
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -312,13 +322,17 @@ class ModelRunner:
         a sequence's keys, the most that any mixer of the group asks for."""
         best = [1] * len(self.cache.paged)
         for i, call in enumerate(self.plan.order):
-            site = self._site_of[i]
-            if site is None:
-                continue
-            kind, gi = self.cache.site_kind(site)
             mixer = getattr(self.plan.layers[call.layer], "mixer", None)
-            if kind == "paged" and mixer is not None:
-                best[gi] = max(best[gi], int(mixer.decode_splits(B, self.max_context, self.cache.page_size, self.dtype)))
+            if mixer is None:
+                continue
+            sites = self._site_of[i]
+            pairs = zip(sites, mixer.members()) if isinstance(sites, list) else [(sites, mixer)]
+            for site, member in pairs:
+                if site is None:
+                    continue
+                kind, gi = self.cache.site_kind(site)
+                if kind == "paged":
+                    best[gi] = max(best[gi], int(member.decode_splits(B, self.max_context, self.cache.page_size, self.dtype)))
         return best
 
     def step_decode_graph(self, entries: Optional[Sequence[StepEntry]], plan=None) -> Optional[torch.Tensor]:

@@ -81,12 +81,16 @@ class ModelPlan:
             pe.bind(tensors, "", dtype)
 
     # ---- caches --------------------------------------------------------------------
-    def cache_sites(self) -> List[Tuple[int, object]]:
-        """(index in the run order, spec) of every call site that owns a cache."""
+    def cache_sites(self) -> List[Tuple[object, object]]:
+        """(site, spec) of every cache that a call site owns.  A site is the call site's index in the run
+        order, or ``(index, member)`` for each member of a mixer that is several mixers side by side (its
+        ``cache_spec`` is a tuple)."""
         out = []
         for i, c in enumerate(self.order):
             if c.cache_of is None:
                 spec = self.layers[c.layer].mixer.cache_spec()
-                if spec is not None:
+                if isinstance(spec, tuple):
+                    out += [((i, j), sp) for j, sp in enumerate(spec) if sp is not None]
+                elif spec is not None:
                     out.append((i, spec))
         return out

@@ -1137,10 +1137,11 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
                      block_table: torch.Tensor, cu_q: torch.Tensor, seqlens_k: torch.Tensor, n: int, num_seqs: int,
                      max_q: int, max_k: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *, window: int = 0,
                      chunk: int = 0, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                     splits: Optional[int] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     splits: Optional[int] = None, status: Optional[torch.Tensor] = None, keep: int = 0) -> torch.Tensor:
     """Causal GQA attention of a mixed batch over the paged cache for keys of width ``dk`` and values
-    of width ``dv``; returns [n, nh*dv].  A query at position p sees key i iff i <= p, i > p - window
-    (``window`` > 0) and i // chunk == p // chunk (``chunk`` > 0).  ``sinks`` [nh] float32 adds
+    of width ``dv``; returns [n, nh*dv].  A query at position p sees key i iff i <= p, (i > p - window or
+    i < keep) (``window`` > 0; ``keep``: the first tokens of a sequence, which a window never leaves behind)
+    and i // chunk == p // chunk (``chunk`` > 0).  ``sinks`` [nh] float32 adds
     exp(sink_h) to head h's softmax denominator; ``gate`` [n, nh] (any row stride) multiplies head
     h's output by sigmoid(gate).  ``cache_layer``: flat pages as for :func:`qk_norm_rope_write_split`."""
     _cuda(q, cache_layer, block_table, cu_q, seqlens_k, sinks, gate)
@@ -1165,7 +1166,7 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
     if splits is None:
         keys = max_k
         if window > 0:
-            keys = min(keys, window + max_q - 1)
+            keys = min(keys, window + max_q - 1 + max(int(keep), 0))
         if chunk > 0:
             keys = min(keys, chunk + max_q - 1)
         splits = masked_attention_splits(num_seqs, max_q, keys, nh, nkv)
@@ -1179,7 +1180,7 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table), block_table.stride(0), _p(cu_q),
         _p(seqlens_k), _p(sinks), _p(gate), ctypes.c_longlong(gate_stride), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, dk, dv, int(page_size), cache_layer.shape[0], ctypes.c_float(scale), int(window), int(chunk),
-        int(splits), _p(status), _stream()),
+        int(splits), _p(status), _stream(), int(keep)),
         2 if splits > 1 or (q.dtype == torch.bfloat16 and dk == dv == 64 and max_q >= 64 and num_seqs > 1) else 1)
     return out
 
@@ -1187,7 +1188,14 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
 def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
                      state_slots: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
                      max_q: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(bias + causal depthwise convolution)`` of ``x`` [n, C] (a column range of a wider tensor
+    """:func:`causal_conv` with SiLU behind it."""
+    return causal_conv(x, taps, bias, state, state_slots, tok_seq, cu_q, positions, max_q, status, act="silu")
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                state_slots: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor,
+                max_q: int, status: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
+    """``act(bias + causal depthwise convolution)`` (``act``: "none" or "silu") of ``x`` [n, C] (a column range of a wider tensor
     is fine: unit inner stride, any row stride) with ``taps`` [L, C] float32, oldest first.  ``state``
     [slots, >= (L-1)*C] float32 holds each request's last L-1 inputs at its front and is moved on.
     Returns [n, C] in x's dtype."""
@@ -1207,10 +1215,12 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.T
         slot_stride, num_slots = state.stride(0), state.shape[0]
     out = torch.empty((n, C), dtype=x.dtype, device=x.device)
     lib = _lib("recurrent")
-    _check(lib, lib.vapi_causal_conv_silu(
+    if act not in ("none", "silu"):
+        raise KernelError(f"activation `{act}` is not one of none, silu")
+    _check(lib, lib.vapi_causal_conv(
         _p(x), ctypes.c_longlong(x.stride(0)), _dt(x), _p(taps), _p(bias), _p(state if L > 1 else None),
         ctypes.c_longlong(slot_stride), _p(state_slots), _p(tok_seq), _p(cu_q), _p(positions), _p(out), n,
-        cu_q.numel() - 1, C, L, num_slots, int(max_q), _p(status), _stream()))
+        cu_q.numel() - 1, C, L, num_slots, int(max_q), 1 if act == "silu" else 0, _p(status), _stream()))
     return out
 
 
@@ -1281,4 +1291,237 @@ def state_space(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bia
         _p(dt_bias), _p(D), ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)), ctypes.c_longlong(state.stride(0)),
         _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, groups, n_state, head, state.shape[0],
         int(min(max_q, 1 << 30)), _p(status), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# several residual streams, mixers side by side, the gated linear recurrence, a mixture of experts
+def embed_sinusoid(table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor],
+                   streams: int = 1, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows of ``table`` [V, H] for ``tokens`` [n] plus a sinusoidal position vector (entry 2i the sine, entry
+    2i+1 the cosine of ``position * freq[i]``; ``freq`` None: nothing is added), as ``streams`` equal copies of
+    the float32 residual stream: [n, streams, H]."""
+    _cuda(table, tokens, positions, freq)
+    _contig(table, "embedding table")
+    _i32(tokens, "tokens")
+    _i32(positions, "positions")
+    _f32(freq, "frequencies")
+    n, (vocab, hidden) = tokens.numel(), table.shape
+    if freq is not None and freq.numel() != (hidden + 1) // 2:
+        raise KernelError(f"{freq.numel()} frequencies for rows of {hidden}")
+    out = torch.empty((n, int(streams), hidden), dtype=torch.float32, device=table.device)
+    lib = _lib("hyper")
+    _check(lib, lib.vapi_embed_sinusoid(_p(table), _dt(table), _p(tokens), _p(positions), _p(freq), _p(out), n, hidden,
+                                        vocab, int(streams), _p(status), _stream()))
+    return out
+
+
+_NORM_KINDS = {"layer": 0, "rms": 1}
+
+
+def hyper_read_norm(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], write: Optional[torch.Tensor],
+                    read: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                    rows: Optional[torch.Tensor] = None, kind: str = "layer") -> Optional[torch.Tensor]:
+    """On the float32 streams ``x`` [n, S, H]: first the pending write of a sublayer's output ``y`` [n, H]
+    (``x_t <- sum_s mix[s, t] x_s + write[t] y`` for all t at once; ``y`` None: nothing pending), then
+    ``u = sum_s read[s] x_s`` (``read`` None: every copy counts once) and its norm with ``weight`` (``kind``
+    "layer": ``(u - mean) / sqrt(var + eps) * w``; "rms": ``u / sqrt(mean u^2 + eps) * w``) in ``out_dtype``.
+    With ``rows`` only those rows are produced and ``x`` is left untouched; ``weight`` None: only the streams
+    are updated (returns None)."""
+    _cuda(x, y, mix, write, read, weight, rows)
+    _f32(x, "residual streams")
+    for t, w in ((mix, "mix matrix"), (write, "write vector"), (read, "read vector"), (weight, "norm weight")):
+        _f32(t, w)
+    _i32(rows, "rows")
+    if x.dim() != 3:
+        raise KernelError("the residual streams must be [n, streams, hidden]")
+    n, S, hidden = x.shape
+    if y is not None:
+        _contig(y, "sublayer output")
+        if y.shape != (n, hidden) or y.dtype != out_dtype:
+            raise KernelError("the sublayer's output must be [n, hidden] of the activation dtype")
+        if mix is None or write is None or mix.numel() != S * S or write.numel() != S:
+            raise KernelError(f"a pending output needs a mix matrix [{S}, {S}] and a write vector [{S}]")
+    if read is not None and read.numel() != S:
+        raise KernelError(f"the read vector must have {S} elements")
+    if weight is not None and weight.numel() != hidden:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {hidden}")
+    n_out = rows.numel() if rows is not None else n
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if weight is not None else None
+    lib = _lib("hyper")
+    _check(lib, lib.vapi_hyper_read_norm(_p(x), _p(y), _DT[out_dtype], _p(mix), _p(write), _p(read), _p(weight),
+                                         ctypes.c_float(eps), _NORM_KINDS[kind], _p(rows), _p(out), n_out, hidden, S,
+                                         _stream()))
+    return out
+
+
+def branch_rmsnorm_mean(branches, weights, eps: float, scale: float) -> torch.Tensor:
+    """``scale * sum_b rmsnorm(branches[b]) * weights[b]`` over up to four [n, H] tensors of one dtype."""
+    _cuda(*branches, *weights)
+    if not 1 <= len(branches) <= 4 or len(weights) != len(branches):
+        raise KernelError("one to four branches, each with its weight")
+    a0 = branches[0]
+    for a, w in zip(branches, weights):
+        _contig(a, "branch output")
+        _f32(w, "norm weight")
+        if a.shape != a0.shape or a.dtype != a0.dtype or w.numel() != a0.shape[1]:
+            raise KernelError("branches must agree in shape and dtype, weights in length")
+    n, hidden = a0.shape
+    out = torch.empty_like(a0)
+    ptrs = (ctypes.c_void_p * len(branches))(*[a.data_ptr() for a in branches])
+    wptrs = (ctypes.c_void_p * len(branches))(*[w.data_ptr() for w in weights])
+    lib = _lib("hyper")
+    _check(lib, lib.vapi_branch_rmsnorm_mean(ptrs, wptrs, len(branches), _dt(a0), ctypes.c_float(eps), ctypes.c_float(scale),
+                                             _p(out), n, hidden, _stream()))
+    return out
+
+
+def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``y * sigmoid(gate)`` for ``y`` [n, width] contiguous and ``gate`` [n, width] of the same dtype (unit inner
+    stride, any row stride: a column range of a wider product)."""
+    _cuda(y, gate)
+    _contig(y, "gated tensor")
+    if gate.shape != y.shape or gate.dtype != y.dtype or gate.stride(1) != 1:
+        raise KernelError("the gate must have the tensor's shape and dtype and unit inner stride")
+    out = torch.empty_like(y)
+    lib = _lib("hyper")
+    _check(lib, lib.vapi_sigmoid_gate(_p(y), _p(gate), ctypes.c_longlong(gate.stride(0)), _dt(y), _p(out), y.shape[0],
+                                      y.shape[1], _stream()))
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x <- cap * tanh(x / cap)`` in place on a contiguous float32 tensor."""
+    _cuda(x)
+    _f32(x, "logits")
+    lib = _lib("hyper")
+    _check(lib, lib.vapi_softcap(_p(x), ctypes.c_float(cap), ctypes.c_longlong(x.numel()), _stream()))
+    return x
+
+
+def rglru(u: torch.Tensor, y: torch.Tensor, w_a: torch.Tensor, b_a: torch.Tensor, w_i: torch.Tensor, b_i: torch.Tensor,
+          lam: torch.Tensor, decay_c: float, state: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
+          cu_q: torch.Tensor, positions: torch.Tensor, status: Optional[torch.Tensor] = None,
+          max_q: int = 1 << 30) -> torch.Tensor:
+    """The real-gated linear recurrent unit over every sequence of the step.  ``u`` [n, C] (contiguous) is the
+    recurrence's input, ``y`` [n, C] (unit inner stride, any row stride) the other branch before its GELU;
+    ``w_a``, ``w_i`` [blocks, C/blocks, C/blocks] (stored [out, in], u's dtype) and ``b_a``, ``b_i`` [C] float32 give
+    ``r = sigmoid(W_a u + b_a)`` and ``i = sigmoid(W_i u + b_i)`` block by block; ``a = exp(-decay_c r softplus(lam))``;
+    ``S <- a S + sqrt(1 - a^2) i u``; returns ``S * gelu_tanh(y)`` [n, C] in u's dtype.  ``state`` [slots, >=
+    state_offset + C] float32 carries S at ``state_offset``."""
+    _cuda(u, y, w_a, b_a, w_i, b_i, lam, state, state_slots, cu_q, positions)
+    _contig(u, "recurrence input")
+    _contig(w_a, "recurrence gate matrix")
+    _contig(w_i, "input gate matrix")
+    for t, w in ((b_a, "gate bias"), (b_i, "gate bias"), (lam, "decay parameter")):
+        _f32(t, w)
+    for t, w in ((state_slots, "state slots"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    n, C = u.shape
+    blocks = w_a.shape[0]
+    if w_a.shape != (blocks, C // blocks, C // blocks) or w_i.shape != w_a.shape or C % blocks:
+        raise KernelError(f"gate matrices {tuple(w_a.shape)} do not fit {C} channels")
+    if w_a.dtype != u.dtype or w_i.dtype != u.dtype or y.dtype != u.dtype:
+        raise KernelError("the gate matrices and the other branch must have the input's dtype")
+    if y.shape != (n, C) or y.stride(1) != 1:
+        raise KernelError("the other branch must be [n, C] with unit inner stride")
+    if b_a.numel() != C or b_i.numel() != C or lam.numel() != C:
+        raise KernelError(f"gate biases and the decay parameter must have {C} elements")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < state_offset + C:
+        raise KernelError("the state must be float32 [slots, >= offset + C] with unit inner stride")
+    a_buf = torch.empty((n, C), dtype=torch.float32, device=u.device)
+    g_buf = torch.empty((n, C), dtype=torch.float32, device=u.device)
+    out = torch.empty((n, C), dtype=u.dtype, device=u.device)
+    lib = _lib("rglru")
+    _check(lib, lib.vapi_rglru(
+        _p(u), ctypes.c_longlong(u.stride(0)), _p(y), ctypes.c_longlong(y.stride(0)), _dt(u), _p(w_a), _p(b_a), _p(w_i),
+        _p(b_i), _p(lam), ctypes.c_float(decay_c), _p(a_buf), _p(g_buf),
+        ctypes.c_void_p(state.data_ptr() + 4 * int(state_offset)), ctypes.c_longlong(state.stride(0)), _p(state_slots),
+        _p(cu_q), _p(positions), _p(out), n, cu_q.numel() - 1, C, blocks, state.shape[0], int(min(max_q, 1 << 30)),
+        _p(status), _stream()), 2)
+    return out
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """``relu(x)^2`` elementwise."""
+    _cuda(x)
+    _contig(x, "activations")
+    out = torch.empty_like(x)
+    lib = _lib("moe")
+    _check(lib, lib.vapi_relu_squared(_p(x), _p(out), _dt(x), ctypes.c_longlong(x.numel()), _stream()))
+    return out
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, experts: int, top: int, groups: int,
+              keep: int):
+    """The router of a mixture of experts for ``h`` [n, W]: ``router`` [outputs, W] and ``correction`` [outputs]
+    float32, ``outputs`` = ``experts`` + identity experts.  Scores are the softmax of the float32 logits over all
+    outputs; the ``top`` largest of score + correction win, among the outputs of the ``keep`` best of ``groups``
+    equal groups of neighbours (a group's score is its largest score + correction); the weights are the chosen
+    scores divided by their sum (+ 1e-20).  Returns ``(ids [n, top] int32, weights [n, top] float32, plan)``;
+    ``plan`` lists the step's (token, choice) pairs expert by expert for :func:`moe_experts`."""
+    _cuda(h, router, correction)
+    _contig(h, "router input")
+    _f32(router, "router matrix")
+    _f32(correction, "router correction")
+    n, W = h.shape
+    outputs = router.shape[0]
+    if router.shape != (outputs, W) or correction.numel() != outputs:
+        raise KernelError("the router must be [outputs, W] and the correction [outputs]")
+    dev = h.device
+    pairs = n * top
+    ids = torch.empty((n, top), dtype=torch.int32, device=dev)
+    wts = torch.empty((n, top), dtype=torch.float32, device=dev)
+    # ranks | counts | offsets | pair_of | number of tiles | tile_expert | tile_row0, one allocation
+    max_tiles = pairs // 64 + max(experts, 1)
+    sizes = [pairs, max(experts, 1), experts + 1, pairs, 1, max_tiles, max_tiles]
+    book = torch.empty((sum(sizes),), dtype=torch.int32, device=dev)
+    parts, at = [], 0
+    for z in sizes:
+        parts.append(book[at:at + z])
+        at += z
+    ranks, counts, offsets, pair_of, ntiles, tile_expert, tile_row0 = parts
+    lib = _lib("moe")
+    _check(lib, lib.vapi_moe_route(_p(h), _dt(h), _p(router), _p(correction), _p(ids), _p(wts), _p(ranks), _p(counts),
+                                   _p(offsets), _p(pair_of), _p(ntiles), _p(tile_expert), _p(tile_row0), n, W, outputs,
+                                   int(experts), int(top), int(groups), int(keep), _stream()), 2 if experts > 0 else 1)
+    return ids, wts, (offsets, pair_of, ntiles, tile_expert, tile_row0)
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_up: Optional[torch.Tensor],
+                w_down: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The weighted sum of the chosen experts' outputs for ``h`` [n, W]: expert e is ``W_down[e] relu(W_up[e] h)^2``
+    with ``w_up`` [experts, ff, W] and ``w_down`` [experts, W, ff] of h's dtype; a choice >= experts is an identity
+    expert (its output is h); ``shared`` [n, W] is added when given.  ``ids``, ``wts``, ``plan``: from
+    :func:`moe_route`."""
+    _cuda(h, ids, wts, w_up, w_down, shared)
+    _contig(h, "expert input")
+    n, W = h.shape
+    top = ids.shape[1]
+    experts = 0 if w_up is None else w_up.shape[0]
+    pairs = n * top
+    y = None
+    lib = _lib("moe")
+    if experts > 0:
+        ff = w_up.shape[1]
+        _contig(w_up, "expert up matrices")
+        _contig(w_down, "expert down matrices")
+        if w_up.shape != (experts, ff, W) or w_down.shape != (experts, W, ff) or w_up.dtype != h.dtype or w_down.dtype != h.dtype:
+            raise KernelError("expert matrices must be [experts, ff, W] and [experts, W, ff] of the input's dtype")
+        offsets, pair_of, ntiles, tile_expert, tile_row0 = plan
+        hid = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
+        y = torch.empty((pairs, W), dtype=torch.float32, device=h.device)
+        _check(lib, lib.vapi_moe_grouped(_p(h), ctypes.c_longlong(h.stride(0)), _p(w_up), _dt(h), _p(ntiles), _p(tile_expert),
+                                         _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(hid), pairs, experts, ff, W,
+                                         top, 0, _stream()))
+        _check(lib, lib.vapi_moe_grouped(_p(hid), ctypes.c_longlong(ff), _p(w_down), _dt(h), _p(ntiles), _p(tile_expert),
+                                         _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(y), pairs, experts, W, ff,
+                                         top, 1, _stream()))
+    if shared is not None:
+        _contig(shared, "shared expert output")
+        if shared.shape != h.shape or shared.dtype != h.dtype:
+            raise KernelError("the shared expert's output must have the input's shape and dtype")
+    out = torch.empty_like(h)
+    _check(lib, lib.vapi_moe_combine(_p(y), _p(ids), _p(wts), _p(h), _p(shared), _p(out), _dt(h), n, W, top, experts,
+                                     _stream()))
     return out

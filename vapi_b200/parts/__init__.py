@@ -2,14 +2,17 @@
 from .base import (CacheView, FeedForward, Mixer, Norm, NormedStream, PagedBuffer, PagedSpec, PostNormed, StreamState, Part, PositionEncoding, StateSpec,
                    TensorSpec, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, make_part,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .rope import RotaryEncoding, ScaledRotaryEncoding
 from .attention import GQAttention
 from .shortconv import ShortConv
-from .recurrent import GatedDeltaMixer, Mamba2Mixer
+from .recurrent import GatedDeltaMixer, Mamba2Mixer, RGLRUMixer
 from .feedforward import SwiGLU
+from .moe import SparseMoE
 from .embedding import OutputHead, TokenEmbedding
 from .block import BLOCKS, PreNormBlock, SandwichBlock, register_block
+from .hyper import HyperBlock, HyperPending
+from .parallel import ParallelMixer
 
 __all__ = [
     "CacheView", "FeedForward", "Mixer", "Norm", "NormedStream", "PagedBuffer", "PagedSpec", "StreamState", "Part", "PositionEncoding", "StateSpec",
@@ -17,4 +20,5 @@ __all__ = [
     "register_feed_forward", "register_mixer", "register_norm", "register_position_encoding",
     "register_block", "RMSNorm", "RotaryEncoding", "GQAttention", "ShortConv", "SwiGLU", "OutputHead",
     "TokenEmbedding", "PreNormBlock", "SandwichBlock", "PostNormed", "ScaledRotaryEncoding", "GatedDeltaMixer", "Mamba2Mixer",
+    "LayerNorm", "RGLRUMixer", "SparseMoE", "HyperBlock", "HyperPending", "ParallelMixer",
 ]

@@ -25,9 +25,12 @@ class GQAttention(Mixer):
     queries and keys), ``chunk`` (a query sees only keys of its own block of ``chunk`` positions,
     counted from position 0), ``sink`` (a learned number per head whose exponential joins the
     softmax's denominator), ``head_gate`` (head h's output times ``sigmoid(W_g x)_h``, the gate's
-    rows riding on the fused projection), ``rope_layout`` ("half": pairs (i, i + rot/2);
+    rows riding on the fused projection), ``keep_first`` (with a window: the first ``keep_first`` tokens of a
+    sequence stay visible to every later query, at their true positions; the pages are then all kept),
+    ``out_gate`` (the concatenated heads times ``sigmoid(W_g x)`` element by element, a gate as wide as the
+    heads' output, its rows riding on the fused projection too), ``rope_layout`` ("half": pairs (i, i + rot/2);
     "interleaved": pairs (2i, 2i+1)) and ``weight_suffix`` (what follows a projection's name in the
-    checkpoint).  Any of the first five sends the mixer to the general kernels
+    checkpoint).  Any of these but the last sends the mixer to the general kernels
     (``ops.qk_norm_rope_write_split``, ``ops.masked_attention``); the plain form keeps the
     specialised ones.
     """
@@ -37,7 +40,7 @@ class GQAttention(Mixer):
                  rot_dim: Optional[int] = None, window: int = 0, bias: bool = False,
                  scale: Optional[float] = None, names: Optional[Dict[str, str]] = None,
                  v_head_dim: Optional[int] = None, chunk: int = 0, sink: bool = False, head_gate: bool = False,
-                 rope_layout: str = "half", weight_suffix: str = ".weight"):
+                 rope_layout: str = "half", weight_suffix: str = ".weight", keep_first: int = 0, out_gate: bool = False):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if rope_layout not in ("half", "interleaved"):
@@ -45,7 +48,11 @@ class GQAttention(Mixer):
         self.dv = int(v_head_dim) if v_head_dim is not None else int(head_dim)
         self.chunk, self.sink, self.head_gate = int(chunk), bool(sink), bool(head_gate)
         self.interleaved = rope_layout == "interleaved"
-        self.general = bool(self.dv != int(head_dim) or self.chunk > 0 or self.sink or self.head_gate or self.interleaved)
+        self.keep_first, self.out_gate = max(int(keep_first), 0) if int(window) > 0 else 0, bool(out_gate)
+        if self.head_gate and self.out_gate:
+            raise ValueError("a gate per head and a gate per element exclude one another")
+        self.general = bool(self.dv != int(head_dim) or self.chunk > 0 or self.sink or self.head_gate or self.interleaved
+                            or self.keep_first > 0 or self.out_gate)
         if self.general:
             if head_dim % 4 or self.dv % 4 or not (4 <= head_dim <= 256 and 4 <= self.dv <= 256):
                 raise ValueError(f"head sizes {head_dim} / {self.dv} must be multiples of 4 in 4..256")
@@ -67,7 +74,9 @@ class GQAttention(Mixer):
 
     def cache_spec(self):
         # (for equal widths this is PagedSpec.kv: keys [nkv, page, d], then values [nkv, page, dv])
-        return PagedSpec((PagedBuffer("k", self.nkv, self.d), PagedBuffer("v", self.nkv, self.dv)), self.window)
+        # (kept first tokens are read for as long as the request lives: nothing is given back early)
+        return PagedSpec((PagedBuffer("k", self.nkv, self.d), PagedBuffer("v", self.nkv, self.dv)),
+                         0 if self.keep_first > 0 else self.window)
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         n, (h, nh, nkv, d), x = self.names, (self.hidden, self.nh, self.nkv, self.d), self.sfx
@@ -75,8 +84,8 @@ class GQAttention(Mixer):
                  TensorSpec(f"{prefix}{n['k']}{x}", (nkv * d, h)),
                  TensorSpec(f"{prefix}{n['v']}{x}", (nkv * self.dv, h)),
                  TensorSpec(f"{prefix}{n['o']}{x}", (h, nh * self.dv))]
-        if self.head_gate:
-            specs.append(TensorSpec(f"{prefix}{n['gate']}{x}", (nh, h)))
+        if self.head_gate or self.out_gate:
+            specs.append(TensorSpec(f"{prefix}{n['gate']}{x}", (nh if self.head_gate else nh * self.dv, h)))
         if self.sink:
             specs.append(TensorSpec(f"{prefix}{n['sink']}", (nh,), role="vector", init="normal"))
         if self.bias:
@@ -92,7 +101,7 @@ class GQAttention(Mixer):
     def bind(self, tensors, prefix, dtype):
         n, x = self.names, self.sfx
         parts = [tensors[f"{prefix}{n[r]}{x}"] for r in ("q", "k", "v")]
-        if self.head_gate:
+        if self.head_gate or self.out_gate:
             parts.append(tensors[f"{prefix}{n['gate']}{x}"])
         wd = parts[0].dtype if all(p.dtype == parts[0].dtype for p in parts) else torch.float32
         if self.general:
@@ -114,7 +123,7 @@ class GQAttention(Mixer):
             self.k_w = tensors[f"{prefix}{n['k_norm']}{x}"].contiguous()
 
     def decode_splits(self, batch: int, max_context: int, page_size: int, dtype: torch.dtype) -> int:
-        keys = min(max_context, self.window) if self.window > 0 else max_context
+        keys = min(max_context, self.window + self.keep_first) if self.window > 0 else max_context
         if self.general:
             if self.chunk > 0:
                 keys = min(keys, self.chunk)
@@ -185,10 +194,14 @@ class GQAttention(Mixer):
             gate = qkv[:, off:off + nh]
         splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
         max_k = getattr(grp, "max_k", None) or ctx.max_k
-        return ops.masked_attention(qkv, qkv.stride(0), pages, page_size, grp.block_table, ctx.cu_q, ctx.seqlens_k,
-                                    ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d, dv, self.scale,
-                                    window=self.window, chunk=self.chunk, sinks=self.sinks, gate=gate, splits=splits,
-                                    status=ctx.status)
+        y = ops.masked_attention(qkv, qkv.stride(0), pages, page_size, grp.block_table, ctx.cu_q, ctx.seqlens_k,
+                                 ctx.n, ctx.num_seqs, ctx.max_q, max_k, nh, nkv, d, dv, self.scale,
+                                 window=self.window, chunk=self.chunk, sinks=self.sinks, gate=gate, splits=splits,
+                                 status=ctx.status, keep=self.keep_first)
+        if self.out_gate:
+            off = (nh + nkv) * d + nkv * dv
+            y = ops.sigmoid_gate(y, qkv[:, off:off + nh * dv])
+        return y
 
 
 register_mixer("gqa_attention", GQAttention)

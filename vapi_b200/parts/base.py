@@ -15,7 +15,7 @@ test (or a new architecture) can add one without touching this package's files.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -120,15 +120,17 @@ class CacheView:
     (page * page_size + offset of each new token) and ``block_table`` [S, width] for the layer's
     group.  ``state``: ``tensor`` is this call site's view [slots, *shape]; ``ctx.state_slots``
     [S] names each sequence's slot.  ``write`` False: the call site reads a cache another layer
-    owns.
+    owns.  ``multi``: the mixer is several mixers side by side (its ``cache_spec`` is a tuple); ``parts`` holds one
+    view per member, in the order of :meth:`Mixer.members`.
     """
 
-    kind: str                 # "paged" | "state" | "none"
+    kind: str                 # "paged" | "state" | "none" | "multi"
     tensor: Optional[torch.Tensor] = None
     group: Any = None
     write: bool = True
     buffers: Optional[Dict[str, torch.Tensor]] = None
     spec: Any = None
+    parts: Optional[List["CacheView"]] = None
 
     def stacked(self) -> torch.Tensor:
         """Buffers of one shape as a single tensor [pages, n_buffers, rows, page_size, width]."""
@@ -227,8 +229,14 @@ class Mixer(Part):
     """Moves information between the tokens of a sequence."""
 
     def cache_spec(self) -> Optional[object]:
-        """A :class:`PagedSpec`, a :class:`StateSpec` or None."""
+        """A :class:`PagedSpec`, a :class:`StateSpec` or None; a mixer made of several mixers side by side
+        returns a tuple with one of these per member (see :meth:`members`), and gets a ``multi``
+        :class:`CacheView` whose ``parts`` are the members' views."""
         return None
+
+    def members(self) -> Sequence["Mixer"]:
+        """The mixers whose caches this mixer's ``cache_spec`` lists: itself, unless it is made of several."""
+        return (self,)
 
     def forward(self, a: torch.Tensor, ctx: "Any", cache: CacheView) -> torch.Tensor:
         """``a`` [n, H] normed activations of every token of the step; returns the layer's

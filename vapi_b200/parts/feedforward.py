@@ -13,10 +13,14 @@ class SwiGLU(FeedForward):
     """``down( silu(gate f) * (up f) )`` without biases; gate and up are stacked into one
     matrix at bind time so they are one product
     (crates/vapi-backend-candle/src/models/lfm2.rs:568-595).  ``names`` maps gate/up/down to
-    the checkpoint's sub-names (LFM2: w1 / w3 / w2)."""
+    the checkpoint's sub-names (LFM2: w1 / w3 / w2).  ``bias``: ``down(silu(gate f + b_g) * (up f + b_u)) + b_d``."""
 
-    def __init__(self, hidden: int, ff: int, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight"):
+    def __init__(self, hidden: int, ff: int, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
+                 bias: bool = False, bias_suffix: str = ".bias"):
         self.hidden, self.ff, self.sfx = int(hidden), int(ff), weight_suffix
+        #: with ``bias`` every projection adds a bias vector (``<name><bias_suffix>``)
+        self.bias, self.bsfx = bool(bias), bias_suffix
+        self.b_gate_up = self.b_down = None
         self.names = {"gate": "w1", "up": "w3", "down": "w2"}
         if names:
             self.names.update(names)
@@ -24,9 +28,14 @@ class SwiGLU(FeedForward):
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         n = self.names
-        return [TensorSpec(f"{prefix}{n['gate']}{self.sfx}", (self.ff, self.hidden)),
-                TensorSpec(f"{prefix}{n['up']}{self.sfx}", (self.ff, self.hidden)),
-                TensorSpec(f"{prefix}{n['down']}{self.sfx}", (self.hidden, self.ff))]
+        specs = [TensorSpec(f"{prefix}{n['gate']}{self.sfx}", (self.ff, self.hidden)),
+                 TensorSpec(f"{prefix}{n['up']}{self.sfx}", (self.ff, self.hidden)),
+                 TensorSpec(f"{prefix}{n['down']}{self.sfx}", (self.hidden, self.ff))]
+        if self.bias:
+            specs += [TensorSpec(f"{prefix}{n['gate']}{self.bsfx}", (self.ff,), role="vector"),
+                      TensorSpec(f"{prefix}{n['up']}{self.bsfx}", (self.ff,), role="vector"),
+                      TensorSpec(f"{prefix}{n['down']}{self.bsfx}", (self.hidden,), role="vector")]
+        return specs
 
     def bind(self, tensors, prefix, dtype):
         n = self.names
@@ -34,11 +43,18 @@ class SwiGLU(FeedForward):
         wd = g.dtype if g.dtype == u.dtype else torch.float32
         self.w_gate_up = torch.cat([g.to(wd), u.to(wd)], 0).contiguous()
         self.w_down = tensors[f"{prefix}{n['down']}{self.sfx}"].contiguous()
+        if self.bias:
+            self.b_gate_up = torch.cat([tensors[f"{prefix}{n['gate']}{self.bsfx}"], tensors[f"{prefix}{n['up']}{self.bsfx}"]], 0).contiguous()
+            self.b_down = tensors[f"{prefix}{n['down']}{self.bsfx}"].contiguous()
 
     def forward(self, f: torch.Tensor, ctx: Any) -> torch.Tensor:
+        if self.bias:
+            return ops.linear(ops.swiglu(ops.linear(f, self.w_gate_up, self.b_gate_up)), self.w_down, self.b_down)
         return ops.linear(ops.linear_swiglu(f, self.w_gate_up), self.w_down)
 
     def forward_stream(self, f, ctx, x, next_weight):
+        if self.bias:
+            return NotImplemented
         n = x.shape[0]
         if not (ops.few_rows_applies(n, self.w_gate_up) and ops.few_rows_applies(n, self.w_down)):
             return NotImplemented

@@ -1,0 +1,77 @@
+"""A mixture of small feed-forward experts with a shared expert and identity experts."""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec, register_feed_forward
+
+
+class SparseMoE(FeedForward):
+    """Each token uses ``top`` of ``experts`` feed-forward layers ``W_down relu(W_up f)^2`` (no biases).
+
+    The router's logits ``W_r f`` are float32 and cover ``experts + identity`` outputs; the scores are their
+    softmax over all outputs.  An output is chosen by its score plus a stored correction; the weights use the
+    score without it, divided by the sum of the chosen scores (+ 1e-20).  The outputs form ``groups`` equal groups
+    of neighbours; a group's score is its largest corrected score, and only outputs of the ``keep`` best groups
+    can be chosen.  The last ``identity`` outputs have no tensors: their output is the token's input itself.  A
+    shared expert of the same form (``shared_ff`` wide; None: absent) runs for every token and is added.
+
+    The experts' matrices are stacked at bind time ([experts, ff, hidden] and [experts, hidden, ff]); a step's
+    tokens are grouped by expert on the device (see ``csrc/moe.cu``), so nothing about the routing reaches the host.
+    """
+
+    def __init__(self, hidden: int, ff: int, experts: int, top: int, *, identity: int = 0, groups: int = 1, keep: int = 1,
+                 shared_ff: Optional[int] = None, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight"):
+        outputs = int(experts) + int(identity)
+        if experts < 0 or identity < 0 or outputs <= 0 or not 1 <= top <= outputs:
+            raise ValueError(f"{experts} experts + {identity} identity experts, top {top}")
+        if groups < 1 or outputs % groups or not 1 <= keep <= groups or (outputs // groups) * keep < top:
+            raise ValueError(f"{outputs} router outputs in {groups} groups, {keep} kept, top {top}")
+        self.hidden, self.ff, self.E, self.I, self.top = int(hidden), int(ff), int(experts), int(identity), int(top)
+        self.groups, self.keep, self.shared_ff, self.sfx = int(groups), int(keep), shared_ff, weight_suffix
+        self.names = {"expert": "experts.{}.", "up": "up_proj", "down": "down_proj", "router": "router",
+                      "correction": "correction", "shared": "shared."}
+        if names:
+            self.names.update(names)
+        self.router = self.correction = self.w_up = self.w_down = self.s_up = self.s_down = None
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        n, h, x = self.names, self.hidden, self.sfx
+        specs = []
+        for e in range(self.E):
+            ep = prefix + n["expert"].format(e)
+            specs += [TensorSpec(f"{ep}{n['up']}{x}", (self.ff, h)), TensorSpec(f"{ep}{n['down']}{x}", (h, self.ff))]
+        # the router works in float32 whatever the activation dtype
+        specs += [TensorSpec(f"{prefix}{n['router']}{x}", (self.E + self.I, h), role="vector"),
+                  TensorSpec(f"{prefix}{n['correction']}", (self.E + self.I,), role="vector", init="zeros")]
+        if self.shared_ff is not None:
+            sp = prefix + n["shared"]
+            specs += [TensorSpec(f"{sp}{n['up']}{x}", (self.shared_ff, h)), TensorSpec(f"{sp}{n['down']}{x}", (h, self.shared_ff))]
+        return specs
+
+    def bind(self, tensors, prefix, dtype):
+        n, x = self.names, self.sfx
+        if self.E > 0:
+            ups = [tensors[f"{prefix}{n['expert'].format(e)}{n['up']}{x}"] for e in range(self.E)]
+            downs = [tensors[f"{prefix}{n['expert'].format(e)}{n['down']}{x}"] for e in range(self.E)]
+            self.w_up = torch.stack([t.to(dtype) for t in ups], 0).contiguous()
+            self.w_down = torch.stack([t.to(dtype) for t in downs], 0).contiguous()
+        self.router = tensors[f"{prefix}{n['router']}{x}"].contiguous()
+        self.correction = tensors[f"{prefix}{n['correction']}"].contiguous()
+        if self.shared_ff is not None:
+            sp = prefix + n["shared"]
+            self.s_up = tensors[f"{sp}{n['up']}{x}"].contiguous()
+            self.s_down = tensors[f"{sp}{n['down']}{x}"].contiguous()
+
+    def forward(self, f: torch.Tensor, ctx: Any) -> torch.Tensor:
+        ids, wts, plan = ops.moe_route(f, self.router, self.correction, self.E, self.top, self.groups, self.keep)
+        shared = None
+        if self.s_up is not None:
+            shared = ops.linear(ops.relu_squared(ops.linear(f, self.s_up)), self.s_down)
+        return ops.moe_experts(f, ids, wts, plan, self.w_up, self.w_down, shared)
+
+
+register_feed_forward("sparse_moe", SparseMoE)

@@ -14,6 +14,9 @@ class RMSNorm(Norm):
     (crates/vapi-backend-candle/src/models/lfm2.rs:626-628).  Mean, rsqrt and the residual
     sum are float32 whatever the activation dtype."""
 
+    #: what the kernels that norm on a reader's behalf call this norm
+    kind = "rms"
+
     def __init__(self, dim: int, eps: float, weight_name: str = "weight"):
         self.dim, self.eps, self.weight_name = int(dim), float(eps), weight_name
         self.weight: Optional[torch.Tensor] = None
@@ -37,4 +40,40 @@ class RMSNorm(Norm):
         return NormedStream(state.xw, state.ss, self.eps)
 
 
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * w`` with a weight and no bias; the variance is the mean of the
+    squared deviations.  Mean, variance and the residual sum are float32 whatever the activation dtype.
+
+    The stream it reads may be a single one, [n, H], with a plain delta pending, or several copies side by
+    side, [n, S, H], with a :class:`~vapi_b200.parts.hyper.HyperPending` pending; it then norms the sum of
+    the copies (that is how a model with several streams ends)."""
+
+    kind = "layer"
+
+    def __init__(self, dim: int, eps: float, weight_name: str = "weight"):
+        self.dim, self.eps, self.weight_name = int(dim), float(eps), weight_name
+        self.weight: Optional[torch.Tensor] = None
+        self._one: Optional[torch.Tensor] = None
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(f"{prefix}{self.weight_name}", (self.dim,), role="vector", init="ones")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], prefix: str, dtype: torch.dtype) -> None:
+        self.weight = tensors[f"{prefix}{self.weight_name}"].contiguous()
+        self._one = torch.ones(1, dtype=torch.float32, device=self.weight.device)
+
+    def apply(self, x, delta, dtype, rows=None):
+        from .hyper import HyperPending
+        if x.dim() == 2:                         # one stream: a plain delta is a write with weight one
+            y = delta.y if isinstance(delta, HyperPending) else delta
+            return ops.hyper_read_norm(x.unsqueeze(1), y, self._one if y is not None else None,
+                                       self._one if y is not None else None, None, self.weight, self.eps, dtype, rows,
+                                       self.kind)
+        if delta is not None and not isinstance(delta, HyperPending):
+            raise TypeError("several streams take a sublayer's output with its mix matrix and write vector")
+        y, mix, write = (delta.y, delta.mix, delta.write) if delta is not None else (None, None, None)
+        return ops.hyper_read_norm(x, y, mix, write, None, self.weight, self.eps, dtype, rows, self.kind)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

@@ -1,4 +1,5 @@
-"""Mixers that carry a fixed-size state per request: the gated delta rule and Mamba-2.
+"""Mixers that carry a fixed-size state per request: the gated delta rule, Mamba-2 and the real-gated
+linear recurrent unit.
 
 Both keep two things in the request's state slot, as one float32 row: the last ``taps - 1``
 inputs of their short causal convolution, and the recurrent matrices of every head.  Their
@@ -176,5 +177,79 @@ class Mamba2Mixer(Mixer):
         return ops.linear(out, self.w_o)
 
 
+class RGLRUMixer(Mixer):
+    """A recurrent block around the real-gated linear recurrent unit (De et al., "Griffin").
+
+    Two branches of ``width`` channels: ``y = gelu_tanh(W_y x + b_y)`` and ``u = conv(W_x x + b_x)``, a causal
+    convolution of ``conv`` taps per channel with bias and no activation.  u is cut into ``blocks`` equal
+    parts; in part b, ``r = sigmoid(R_a[b] u_b + b_a[b])`` and ``i = sigmoid(R_i[b] u_b + b_i[b])`` with square
+    matrices stored [out, in].  Per channel
+
+        log a = -decay_c * r * softplus(lam);   S <- exp(log a) S + sqrt(1 - a^2) (i u)
+
+    from S = 0 at position 0, and the block returns ``W_o (S * y)``.  The request's state slot holds the
+    convolution's last ``conv - 1`` inputs and S, as one float32 row.  The two in-projections are one product.
+    """
+
+    def __init__(self, hidden: int, width: int, blocks: int, conv: int, *, decay_c: float = 8.0,
+                 names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
+        if width <= 0 or blocks <= 0 or width % blocks:
+            raise ValueError(f"{width} channels do not split into {blocks} equal parts")
+        if not 1 <= conv <= 8:
+            raise ValueError(f"convolution of {conv} taps is outside 1..8")
+        self.hidden, self.C, self.B, self.L = int(hidden), int(width), int(blocks), int(conv)
+        self.decay_c, self.sfx, self.bsfx = float(decay_c), weight_suffix, bias_suffix
+        self.names = {"y": "y_proj", "x": "x_proj", "conv": "conv1d", "a": "a_gate", "i": "input_gate", "lam": "a_param",
+                      "o": "out_proj"}
+        if names:
+            self.names.update(names)
+        self.conv_elems = (self.L - 1) * self.C
+        self.w_in = self.b_in = self.taps = self.conv_b = self.w_a = self.b_a = self.w_i = self.b_i = self.lam = self.w_o = None
+
+    def cache_spec(self):
+        return StateSpec("rglru", (self.conv_elems + self.C,), torch.float32)
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        n, h, C, B, x, b = self.names, self.hidden, self.C, self.B, self.sfx, self.bsfx
+        bs = C // B
+        return [TensorSpec(f"{prefix}{n['y']}{x}", (C, h)), TensorSpec(f"{prefix}{n['y']}{b}", (C,), role="vector"),
+                TensorSpec(f"{prefix}{n['x']}{x}", (C, h)), TensorSpec(f"{prefix}{n['x']}{b}", (C,), role="vector"),
+                TensorSpec(f"{prefix}{n['conv']}{x}", (C, self.L), role="vector"),
+                TensorSpec(f"{prefix}{n['conv']}{b}", (C,), role="vector"),
+                TensorSpec(f"{prefix}{n['a']}{x}", (B, bs, bs)), TensorSpec(f"{prefix}{n['a']}{b}", (B, bs), role="vector"),
+                TensorSpec(f"{prefix}{n['i']}{x}", (B, bs, bs)), TensorSpec(f"{prefix}{n['i']}{b}", (B, bs), role="vector"),
+                TensorSpec(f"{prefix}{n['lam']}", (C,), role="vector"),
+                TensorSpec(f"{prefix}{n['o']}{x}", (h, C))]
+
+    def bind(self, tensors, prefix, dtype):
+        n, x, b = self.names, self.sfx, self.bsfx
+        wy, wx = tensors[f"{prefix}{n['y']}{x}"], tensors[f"{prefix}{n['x']}{x}"]
+        wd = wy.dtype if wy.dtype == wx.dtype else torch.float32
+        self.w_in = torch.cat([wy.to(wd), wx.to(wd)], 0).contiguous()                     # y | x
+        self.b_in = torch.cat([tensors[f"{prefix}{n['y']}{b}"], tensors[f"{prefix}{n['x']}{b}"]], 0).contiguous()
+        self.taps = _taps(tensors[f"{prefix}{n['conv']}{x}"])
+        self.conv_b = tensors[f"{prefix}{n['conv']}{b}"].contiguous()
+        # the gates are computed in float32 from matrices kept in the activation dtype
+        self.w_a = tensors[f"{prefix}{n['a']}{x}"].to(dtype).contiguous()
+        self.w_i = tensors[f"{prefix}{n['i']}{x}"].to(dtype).contiguous()
+        self.b_a = tensors[f"{prefix}{n['a']}{b}"].reshape(-1).contiguous()
+        self.b_i = tensors[f"{prefix}{n['i']}{b}"].reshape(-1).contiguous()
+        self.lam = tensors[f"{prefix}{n['lam']}"].contiguous()
+        self.w_o = tensors[f"{prefix}{n['o']}{x}"].contiguous()
+
+    def forward(self, a: torch.Tensor, ctx: Any, cache: CacheView) -> torch.Tensor:
+        C = self.C
+        h = ops.linear(a, self.w_in, self.b_in)
+        if h.dtype != a.dtype:
+            h = h.to(a.dtype)
+        state = cache.tensor
+        u = ops.causal_conv(h[:, C:], self.taps, self.conv_b, state, ctx.state_slots, ctx.tok_seq, ctx.cu_q,
+                            ctx.positions, ctx.max_q, ctx.status, act="none")
+        s = ops.rglru(u, h[:, :C], self.w_a, self.b_a, self.w_i, self.b_i, self.lam, self.decay_c, state, self.conv_elems,
+                      ctx.state_slots, ctx.cu_q, ctx.positions, ctx.status, max_q=ctx.max_q)
+        return ops.linear(s, self.w_o)
+
+
 register_mixer("gated_delta", GatedDeltaMixer)
+register_mixer("rglru", RGLRUMixer)
 register_mixer("mamba2", Mamba2Mixer)
