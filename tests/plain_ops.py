@@ -523,27 +523,29 @@ def softcap(x, cap):
 
 
 def rglru(u, y, w_a, b_a, w_i, b_i, lam, decay_c, state, state_offset, state_slots, cu_q, positions, status=None, max_q=1):
+    """(In float64: 1 - a^2 loses most of its digits in float32 when a is close to 1, and a reference should not.)"""
     n, C = u.shape
     B = w_a.shape[0]
     bs = C // B
-    out = torch.zeros((n, C), dtype=torch.float32)
-    sp = _softplus(lam)
+    d = torch.float64
+    out = torch.zeros((n, C), dtype=d)
+    sp = _softplus(lam.to(d))
     for s in range(cu_q.numel() - 1):
         r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
         if r1 == r0:
             continue
         slot = int(state_slots[s])
-        S = state[slot, state_offset:state_offset + C].clone() if int(positions[r0]) > 0 else torch.zeros(C)
+        S = state[slot, state_offset:state_offset + C].to(d) if int(positions[r0]) > 0 else torch.zeros(C, dtype=d)
         for r in range(r0, r1):
-            ur = _f(u[r])
-            ga = torch.cat([_f(w_a[b]) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_a
-            gi = torch.cat([_f(w_i[b]) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_i
+            ur = u[r].to(d)
+            ga = torch.cat([w_a[b].to(d) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_a.to(d)
+            gi = torch.cat([w_i[b].to(d) @ ur[b * bs:(b + 1) * bs] for b in range(B)]) + b_i.to(d)
             log_a = -decay_c * torch.sigmoid(ga) * sp
             a = torch.exp(log_a)
             S = a * S + torch.sqrt(torch.clamp(1.0 - a * a, min=0.0)) * torch.sigmoid(gi) * ur
-            yr = _f(y[r])
+            yr = y[r].to(d)
             out[r] = S * (0.5 * yr * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (yr + 0.044715 * yr ** 3))))
-        state[slot, state_offset:state_offset + C] = S
+        state[slot, state_offset:state_offset + C] = S.to(state.dtype)
     return out.to(u.dtype)
 
 
