@@ -120,14 +120,27 @@ def part_tensors(plan):
     from vapi_b200.parts.base import Part
     seen = set()
 
+    def members(v):
+        """A part's attribute, or what a list or dictionary in it holds."""
+        if isinstance(v, (list, tuple)):
+            for x in v:
+                yield from members(x)
+        elif isinstance(v, dict):
+            for x in v.values():
+                yield from members(x)
+        else:
+            yield v
+
     def of_part(part):
-        for name, v in vars(part).items():
-            if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                seen.add(v.data_ptr())
-                yield f"{type(part).__name__}.{name}", v
-        for v in vars(part).values():
-            if isinstance(v, Part):
-                yield from of_part(v)
+        for name, held in vars(part).items():
+            for v in members(held):
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    yield f"{type(part).__name__}.{name}", v
+        for held in vars(part).values():
+            for v in members(held):
+                if isinstance(v, Part):
+                    yield from of_part(v)
 
     for call in plan.order:
         yield from of_part(plan.layers[call.layer])
@@ -184,7 +197,10 @@ OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens
        "shortconv": "shortconv", "sample_rows": "sampling", "sample_truncated": "sampling", "linear": "library",
        "postnorm_add_rmsnorm": "elementwise", "gated_group_rmsnorm": "elementwise", "scale_rows": "elementwise",
        "rope_cos_sin_scaled": "rope", "qk_norm_rope_write_split": "rope", "masked_attention": "attention_masked",
-       "causal_conv_silu": "recurrent", "gated_delta": "recurrent", "state_space": "recurrent"}
+       "causal_conv_silu": "recurrent", "gated_delta": "recurrent", "state_space": "recurrent",
+       "embed_sinusoid": "hyper", "hyper_read_norm": "hyper", "branch_rmsnorm_mean": "hyper", "sigmoid_gate": "hyper",
+       "softcap": "hyper", "causal_conv": "recurrent", "rglru": "rglru", "relu_squared": "moe", "moe_route": "moe",
+       "moe_experts": "moe"}
 
 
 class OpLog:
@@ -233,7 +249,7 @@ class OpLog:
                 # what an elementwise call moves: its activations in and out (not the caches and states it
                 # touches a few rows of, not the plan's own tensors)
                 moved = sum(t.numel() * t.element_size() for t in tensors + outs
-                            if t.dim() <= 2 and t.data_ptr() not in self.labels)
+                            if t.dim() <= 3 and t.data_ptr() not in self.labels)
                 if name == "embed":
                     moved *= 2            # the rows gathered from the table, and the stream written
                 self.calls.append({"op": name, "weight": weight[0] if weight else None,
@@ -743,9 +759,31 @@ def vukavik_sizes(name):
     return vk, lf
 
 
+def rapolix_sizes(name):
+    """Rapolix layers at the widths of LFM2-<name>: two residual streams; in every layer attention with the same
+    heads as the LFM2 stack (keys and values of 64) over a window of 1,024 that keeps the first four tokens, beside
+    a recurrent block as wide as the model in parts of 256 with a convolution of four taps; feed-forwards
+    alternate between a dense one of the LFM2 stack's width and a mixture of 30 experts and 2 identity experts
+    (a quarter of that width each, four of them a token, from two of four groups) with a shared expert; eight layers."""
+    from vapi_b200.models.lfm2 import Lfm2Config
+    lf = lfm2_sizes(name)
+    W, ff = lf["hidden_size"], Lfm2Config.effective_ff_dim(lf)
+    mixer = {"left": {"heads": lf["num_attention_heads"], "kv_heads": lf["num_key_value_heads"], "dim": 64, "vdim": 64,
+                      "scale": 0.125, "mask": {"size": 1024, "keep_first": 4}},
+             "right": {"width": W, "blocks": W // 256, "conv": 4}}
+    dense = {"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+    sparse = {"type": "parallel", "mixer": mixer, "mlp": {
+        "kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+        "router": {"experts": 30, "identity": 2, "top": 4, "groups": {"count": 4, "keep": 2}}}}
+    rp = {"architecture": "Rapolix", "vocab": lf["vocab_size"], "width": W, "streams": 2, "logit_softcap": 30.0,
+          "norm": {"eps": 1e-5}, "layers": [dense, sparse] * 4}
+    lf = dict(lf, num_hidden_layers=8, layer_types=["conv", "conv", "conv", "full_attention"] * 2)
+    return rp, lf
+
+
 def mixers(args):
-    """``--only mixers``: prefill and decode of Vukavik layers beside LFM2 layers of equal width (random
-    weights, eight layers each), and where each model's time goes, kernel family by kernel family."""
+    """``--only mixers``: prefill and decode of eight layers of ``--design`` (Vukavik or Rapolix) beside LFM2 layers
+    of equal width (random weights), and where each model's time goes, kernel family by kernel family."""
     import torch
     from vapi_b200 import ops
     from vapi_b200.engine.runner import ModelRunner
@@ -758,8 +796,9 @@ def mixers(args):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     out = {"only": "mixers", "sizes": args.sizes, "dtype": "bfloat16", "prefill_tokens": T, "decode_batch": B,
            "decode_context": ctx_len, "peaks": pk, "models": {}}
-    vk, lf = vukavik_sizes(args.sizes)
-    for name, cfg in (("vukavik", vk), ("lfm2", lf)):
+    vk, lf = rapolix_sizes(args.sizes) if args.design == "rapolix" else vukavik_sizes(args.sizes)
+    out["design"] = args.design
+    for name, cfg in ((args.design, vk), ("lfm2", lf)):
         vocab = cfg.get("vocab") or cfg["vocab_size"]
         n_pages = (B + 1) * (-(-(ctx_len + 64) // page)) + 8
         runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=n_pages, page_size=page,
@@ -798,9 +837,19 @@ def mixers(args):
         # arithmetic of the mixers' own kernels for one prompt of T tokens, per call
         mix_flops = {}
         for blk in runner.plan.layers:
-            m = blk.mixer
+            ffn = getattr(blk, "ffn", None)
+            if type(ffn).__name__ == "SparseMoE":
+                mix_flops["moe_experts"] = 2.0 * 2 * ffn.top * ffn.ff * ffn.hidden * T      # as if every choice were an expert
+                mix_flops["moe_route"] = 2.0 * (ffn.E + ffn.I) * ffn.hidden * T
+        for blk in runner.plan.layers:
+          for m in blk.mixer.members():
             kind = type(m).__name__
-            if kind == "GQAttention":
+            if kind == "GQAttention" and getattr(m, "window", 0) > 0 and not getattr(m, "chunk", 0):
+                pairs = sum(min(t + 1, m.window + min(m.keep_first, max(0, t + 1 - m.window))) for t in range(T))
+                mix_flops["masked_attention" if m.general else "paged_attention"] = 2.0 * m.nh * (m.d + m.dv) * pairs
+            elif kind == "RGLRUMixer":
+                mix_flops["rglru"] = 2.0 * 2 * m.C * (m.C // m.B) * T                        # the two gates' products
+            elif kind == "GQAttention":
                 span = min(T, m.chunk) if getattr(m, "chunk", 0) else T
                 pairs = (T // span) * span * (span + 1) / 2 + (T % span) * (T % span + 1) / 2
                 mix_flops["masked_attention" if getattr(m, "general", False) else "paged_attention"] = 2.0 * m.nh * (m.d + getattr(m, "dv", m.d)) * pairs
@@ -908,6 +957,8 @@ def main():
                          "and print what one step's kernels did inside the captured graph, or (mixers) prefill and "
                          "decode of eight Vukavik layers beside eight LFM2 layers of equal width, kernel family by kernel family")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
+    ap.add_argument("--design", default="vukavik", choices=["vukavik", "rapolix"],
+                    help="with --only mixers: the architecture whose layers stand beside LFM2's")
     ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--dtype", default="bfloat16", help="bfloat16 (serving) or float32 (the true 32-bit path)")
     ap.add_argument("--no-fp32", action="store_true", help="leave the float32 points out of the default run")
