@@ -485,10 +485,14 @@ def embed_sinusoid(table, tokens, positions, freq, streams=1, status=None):
     return x[:, None, :].repeat(1, streams, 1).contiguous()
 
 
-def hyper_read_norm(x, y, mix, write, read, weight, eps, out_dtype, rows=None, kind="layer"):
-    """x [n, S, H]: the pending write (x_t <- sum_s mix[s, t] x_s + write[t] y), then the norm of sum_s read[s] x_s."""
+def hyper_read_norm(x, y, mix, write, read, weight, eps, out_dtype, rows=None, kind="layer", branch=None):
+    """x [n, S, H]: the pending write (x_t <- sum_s mix[s, t] x_s + write[t] y), then the norm of sum_s read[s] x_s.
+    branch = (y2, w_y, w_y2, eps, scale): y stands for scale * (rms(y) w_y + rms(y2) w_y2)."""
     n, S, H = x.shape
     new = x
+    if branch is not None:
+        y2, wy, wy2, eps_y, scale = branch
+        y = branch_rmsnorm_mean([y] + ([y2] if y2 is not None else []), [wy] + ([wy2] if y2 is not None else []), eps_y, scale)
     if y is not None:
         new = torch.einsum("st,nsh->nth", mix.reshape(S, S), x) + write.reshape(1, S, 1) * _f(y)[:, None, :]
         if rows is None:

@@ -154,6 +154,18 @@ def test_streams_read_norm_and_embedding_kernels(dtype):
                                                   rr.cuda() if rr is not None else None, kind)
                         _close(got, want, tol)
                         _close(xb, xa, 1e-6)            # the streams themselves are float32 either way
+        # two mixers' outputs whose own norms and mean ride on the read
+        y2, wy, wy2 = (torch.randn((n, H), generator=g) * 7).to(dtype), 1 + 0.2 * torch.randn(H, generator=g), 1 + 0.2 * torch.randn(H, generator=g)
+        for second in (True, False):
+            for rr in (None, rows):
+                xa, xb = x.clone(), x.clone().cuda()
+                want = plain_ops.hyper_read_norm(xa, y, mix, write, read, w, 1e-5, dtype, rr, "layer",
+                                                 (y2 if second else None, wy, wy2 if second else None, 1e-6, 0.5))
+                got = ops.hyper_read_norm(xb, y.cuda(), mix.cuda().contiguous(), write.cuda(), read.cuda(), w.cuda(), 1e-5, dtype,
+                                          rr.cuda() if rr is not None else None, "layer",
+                                          (y2.cuda() if second else None, wy.cuda(), wy2.cuda() if second else None, 1e-6, 0.5))
+                _close(got, want, tol)
+                _close(xb, xa, 1e-6 if dtype == torch.float32 else 2e-2)
         xa, xb = x.clone(), x.clone().cuda()
         assert ops.hyper_read_norm(xb, y.cuda(), mix.cuda().contiguous(), write.cuda(), None, None, 1e-5, dtype) is None
         plain_ops.hyper_read_norm(xa, y, mix, write, None, None, 1e-5, dtype)

@@ -66,30 +66,73 @@ VAPI_EXPORT int vapi_embed_sinusoid(const void* table, int dtype, const int* tok
     return check_launch("embed_sinusoid", e);
 }
 
-// One block a wanted row.  y (may be null: nothing pending), mix [S, S] indexed [from, to], write [S],
+// What is pending may also be two mixers' outputs that still want their own RMS norms and their mean:
+// y = y_scale * (rms(y) * wy + rms(y2) * wy2)  (wy null: y as it is; y2 null: one branch).
+struct HyperArgs {
+    const float* mix; const float* write; const float* read;      // [S, S] indexed [from, to]; [S]; [S] (null: ones)
+    const float* w; float eps; int kind;                          // the reader's norm (w null: only update the streams)
+    const float* wy; const float* wy2; float eps_y; float y_scale;
+    const int* rows; int n_out, hidden, streams, write_x;
+};
+
+template <typename T> struct Ld4T;
+template <> struct Ld4T<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Ld4T<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&a);
+        u.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+// One block a wanted row, any sizes.  y (may be null: nothing pending), mix [S, S] indexed [from, to], write [S],
 // read [S] (null: every copy counts once).  With `rows` the streams are left as they are (the pending
 // write is applied on the fly).  w null: only the streams are updated.
 template <typename T>
-__global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mix,
-                                       const float* __restrict__ write, const float* __restrict__ read,
-                                       const float* __restrict__ w, float eps, int kind, const int* __restrict__ rows,
-                                       T* __restrict__ out, int n_out, int hidden, int streams, int write_x) {
+__global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const T* __restrict__ y2, HyperArgs p,
+                                       T* __restrict__ out) {
     extern __shared__ float hc_row[];          // the row u, [hidden]
     __shared__ float red[33];
     __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_write[HC_MAX_STREAMS], s_read[HC_MAX_STREAMS];
     const int j = blockIdx.x;
+    const int streams = p.streams, hidden = p.hidden;
     pdl_trigger();
-    if (threadIdx.x < streams * streams) s_mix[threadIdx.x] = (y && mix) ? mix[threadIdx.x] : 0.f;
+    if (threadIdx.x < streams * streams) s_mix[threadIdx.x] = (y && p.mix) ? p.mix[threadIdx.x] : 0.f;
     if (threadIdx.x < streams) {
-        s_write[threadIdx.x] = (y && write) ? write[threadIdx.x] : 0.f;
-        s_read[threadIdx.x] = read ? read[threadIdx.x] : 1.f;
+        s_write[threadIdx.x] = (y && p.write) ? p.write[threadIdx.x] : 0.f;
+        s_read[threadIdx.x] = p.read ? p.read[threadIdx.x] : 1.f;
     }
     pdl_wait();
-    if (j >= n_out) return;
+    if (j >= p.n_out) return;
     __syncthreads();
-    const int row = rows ? rows[j] : j;
+    const int row = p.rows ? p.rows[j] : j;
     float* xr = x + (size_t)row * streams * hidden;
     const T* yr = y ? y + (size_t)row * hidden : nullptr;
+    const T* yr2 = y2 ? y2 + (size_t)row * hidden : nullptr;
+    float inv1 = 1.f, inv2 = 0.f;
+    if (yr && p.wy) {
+        float s1 = 0.f, s2 = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float a = to_f32(yr[c]), b = yr2 ? to_f32(yr2[c]) : 0.f;
+            s1 += a * a;
+            s2 += b * b;
+        }
+        s1 = block_sum(s1, red);
+        s2 = block_sum(s2, red);
+        inv1 = rsqrtf(s1 / (float)hidden + p.eps_y);
+        inv2 = rsqrtf(s2 / (float)hidden + p.eps_y);
+    }
     float sum = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float old[HC_MAX_STREAMS];
@@ -97,7 +140,12 @@ __global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restric
         for (int s = 0; s < HC_MAX_STREAMS; ++s) old[s] = s < streams ? xr[(size_t)s * hidden + c] : 0.f;
         float u = 0.f;
         if (yr) {
-            const float yv = to_f32(yr[c]);
+            float yv = to_f32(yr[c]);
+            if (p.wy) {
+                yv = yv * inv1 * p.wy[c];
+                if (yr2) yv += to_f32(yr2[c]) * inv2 * p.wy2[c];
+                yv = round_to<T>(yv * p.y_scale);       // what a kernel of its own would have stored
+            }
 #pragma unroll
             for (int t = 0; t < HC_MAX_STREAMS; ++t) {
                 if (t < streams) {
@@ -105,7 +153,7 @@ __global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restric
 #pragma unroll
                     for (int s = 0; s < HC_MAX_STREAMS; ++s)
                         if (s < streams) v = fmaf(s_mix[s * streams + t], old[s], v);
-                    if (write_x) xr[(size_t)t * hidden + c] = v;
+                    if (p.write_x) xr[(size_t)t * hidden + c] = v;
                     u = fmaf(s_read[t], v, u);
                 }
             }
@@ -115,12 +163,12 @@ __global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restric
                 if (t < streams) u = fmaf(s_read[t], old[t], u);
         }
         hc_row[c] = u;
-        sum += kind == 0 ? u : u * u;
+        sum += p.kind == 0 ? u : u * u;
     }
-    if (!w) return;
+    if (!p.w) return;
     sum = block_sum(sum, red);
     float mean = 0.f, inv;
-    if (kind == 0) {
+    if (p.kind == 0) {
         mean = sum / (float)hidden;
         float dev = 0.f;
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
@@ -128,42 +176,184 @@ __global__ void hyper_read_norm_kernel(float* __restrict__ x, const T* __restric
             dev += d * d;
         }
         dev = block_sum(dev, red);
-        inv = rsqrtf(dev / (float)hidden + eps);
+        inv = rsqrtf(dev / (float)hidden + p.eps);
     } else {
-        inv = rsqrtf(sum / (float)hidden + eps);
+        inv = rsqrtf(sum / (float)hidden + p.eps);
     }
     T* orow = out + (size_t)j * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) orow[c] = from_f32<T>((hc_row[c] - mean) * inv * w[c]);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) orow[c] = from_f32<T>((hc_row[c] - mean) * inv * p.w[c]);
 }
 
-VAPI_EXPORT int vapi_hyper_read_norm(float* x, const void* y, int dtype, const float* mix, const float* write,
-                                     const float* read, const float* w, float eps, int kind, const int* rows, void* out,
-                                     int n_out, int hidden, int streams, cudaStream_t stream) {
+// The same with 16-byte accesses and the row u held in registers between the passes, for S streams known at
+// compile time and hidden a multiple of 4, at most 4 * HC_KMAX * blockDim.
+constexpr int HC_KMAX = 4;
+template <typename T, int S>
+__global__ void hyper_read_norm_vec_kernel(float* __restrict__ x, const T* __restrict__ y, const T* __restrict__ y2, HyperArgs p,
+                                           T* __restrict__ out) {
+    __shared__ float red[33];
+    __shared__ float s_mix[S * S], s_write[S], s_read[S];
+    const int j = blockIdx.x;
+    const int hidden = p.hidden, h4 = hidden >> 2;
+    pdl_trigger();
+    if (threadIdx.x < S * S) s_mix[threadIdx.x] = (y && p.mix) ? p.mix[threadIdx.x] : 0.f;
+    if (threadIdx.x < S) {
+        s_write[threadIdx.x] = (y && p.write) ? p.write[threadIdx.x] : 0.f;
+        s_read[threadIdx.x] = p.read ? p.read[threadIdx.x] : 1.f;
+    }
+    pdl_wait();
+    if (j >= p.n_out) return;
+    __syncthreads();
+    const int row = p.rows ? p.rows[j] : j;
+    float* xr = x + (size_t)row * S * hidden;
+    const T* yr = y ? y + (size_t)row * hidden : nullptr;
+    const T* yr2 = y2 ? y2 + (size_t)row * hidden : nullptr;
+    float inv1 = 1.f, inv2 = 0.f;
+    if (yr && p.wy) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < HC_KMAX; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < h4) {
+                const float4 a = Ld4T<T>::load(yr + 4 * c);
+                s1 += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                if (yr2) {
+                    const float4 b = Ld4T<T>::load(yr2 + 4 * c);
+                    s2 += b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+                }
+            }
+        }
+        s1 = block_sum(s1, red);
+        s2 = block_sum(s2, red);
+        inv1 = rsqrtf(s1 / (float)hidden + p.eps_y);
+        inv2 = rsqrtf(s2 / (float)hidden + p.eps_y);
+    }
+    float4 u4[HC_KMAX];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < HC_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        u4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c >= h4) continue;
+        float old[S][4];
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            const float4 v = Ld4T<float>::load(xr + (size_t)s * hidden + 4 * c);
+            old[s][0] = v.x; old[s][1] = v.y; old[s][2] = v.z; old[s][3] = v.w;
+        }
+        float uu[4] = {0.f, 0.f, 0.f, 0.f};
+        if (yr) {
+            const float4 ya = Ld4T<T>::load(yr + 4 * c);
+            float yv[4] = {ya.x, ya.y, ya.z, ya.w};
+            if (p.wy) {
+                const float4 wa = Ld4T<float>::load(p.wy + 4 * c);
+                const float wv[4] = {wa.x, wa.y, wa.z, wa.w};
+                float bv[4] = {0.f, 0.f, 0.f, 0.f}, w2[4] = {0.f, 0.f, 0.f, 0.f};
+                if (yr2) {
+                    const float4 yb = Ld4T<T>::load(yr2 + 4 * c), wb = Ld4T<float>::load(p.wy2 + 4 * c);
+                    bv[0] = yb.x; bv[1] = yb.y; bv[2] = yb.z; bv[3] = yb.w;
+                    w2[0] = wb.x; w2[1] = wb.y; w2[2] = wb.z; w2[3] = wb.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = yv[e] * inv1 * wv[e];
+                    if (yr2) v += bv[e] * inv2 * w2[e];
+                    yv[e] = round_to<T>(v * p.y_scale);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < S; ++t) {
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v[e] = s_write[t] * yv[e];
+#pragma unroll
+                    for (int s = 0; s < S; ++s) v[e] = fmaf(s_mix[s * S + t], old[s][e], v[e]);
+                    uu[e] = fmaf(s_read[t], v[e], uu[e]);
+                }
+                if (p.write_x) Ld4T<float>::store(xr + (size_t)t * hidden + 4 * c, make_float4(v[0], v[1], v[2], v[3]));
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < S; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) uu[e] = fmaf(s_read[t], old[t][e], uu[e]);
+        }
+        u4[k] = make_float4(uu[0], uu[1], uu[2], uu[3]);
+        sum += p.kind == 0 ? (uu[0] + uu[1]) + (uu[2] + uu[3]) : uu[0] * uu[0] + uu[1] * uu[1] + uu[2] * uu[2] + uu[3] * uu[3];
+    }
+    if (!p.w) return;
+    sum = block_sum(sum, red);
+    float mean = 0.f, inv;
+    if (p.kind == 0) {
+        mean = sum / (float)hidden;
+        float dev = 0.f;
+#pragma unroll
+        for (int k = 0; k < HC_KMAX; ++k) {
+            if ((int)(threadIdx.x + k * blockDim.x) < h4) {
+                const float a = u4[k].x - mean, b = u4[k].y - mean, c = u4[k].z - mean, d = u4[k].w - mean;
+                dev += a * a + b * b + c * c + d * d;
+            }
+        }
+        dev = block_sum(dev, red);
+        inv = rsqrtf(dev / (float)hidden + p.eps);
+    } else {
+        inv = rsqrtf(sum / (float)hidden + p.eps);
+    }
+    T* orow = out + (size_t)j * hidden;
+#pragma unroll
+    for (int k = 0; k < HC_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < h4) {
+            const float4 wv = Ld4T<float>::load(p.w + 4 * c);
+            Ld4T<T>::store(orow + 4 * c, make_float4((u4[k].x - mean) * inv * wv.x, (u4[k].y - mean) * inv * wv.y,
+                                                     (u4[k].z - mean) * inv * wv.z, (u4[k].w - mean) * inv * wv.w));
+        }
+    }
+}
+
+template <typename T>
+static int launch_hyper(float* x, const void* y, const void* y2, const HyperArgs& p, void* out, cudaStream_t stream) {
+    const int hidden = p.hidden;
+    cudaError_t e;
+    const int vt = hidden >= 2048 ? 256 : 128;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)y2 | (uintptr_t)out | (uintptr_t)p.w | (uintptr_t)p.wy |
+                           (uintptr_t)p.wy2) & 15) == 0;
+    if (hidden % 4 == 0 && hidden / 4 <= HC_KMAX * vt && p.streams <= 4 && aligned) {
+#define HC_VEC(S) e = launch(hyper_read_norm_vec_kernel<T, S>, p.n_out, vt, 0, stream, x, (const T*)y, (const T*)y2, p, (T*)out)
+        if (p.streams == 1) HC_VEC(1);
+        else if (p.streams == 2) HC_VEC(2);
+        else if (p.streams == 3) HC_VEC(3);
+        else HC_VEC(4);
+#undef HC_VEC
+        return check_launch("hyper_read_norm", e);
+    }
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return fail(-1, "hyper_read_norm: rows of %d do not fit shared memory", hidden);
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    auto kern = hyper_read_norm_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = launch(kern, p.n_out, threads, smem, stream, x, (const T*)y, (const T*)y2, p, (T*)out);
+    return check_launch("hyper_read_norm", e);
+}
+
+VAPI_EXPORT int vapi_hyper_read_norm(float* x, const void* y, const void* y2, int dtype, const float* wy, const float* wy2,
+                                     float eps_y, float y_scale, const float* mix, const float* write, const float* read,
+                                     const float* w, float eps, int kind, const int* rows, void* out, int n_out, int hidden,
+                                     int streams, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (hidden <= 0 || streams < 1 || streams > HC_MAX_STREAMS)
         return fail(-1, "hyper_read_norm: hidden=%d streams=%d (at most %d)", hidden, streams, HC_MAX_STREAMS);
     if (y && (!mix || !write)) return fail(-1, "hyper_read_norm: a pending output needs its mix matrix and write vector");
+    if (y2 && (!y || !wy || !wy2)) return fail(-1, "hyper_read_norm: a second branch needs the first and both norm weights");
     if (w && !out) return fail(-1, "hyper_read_norm: a norm needs an output");
     if (kind != 0 && kind != 1) return fail(-1, "hyper_read_norm: norm kind %d", kind);
-    const size_t smem = (size_t)hidden * sizeof(float);
-    if (smem > 200 * 1024) return fail(-1, "hyper_read_norm: rows of %d do not fit shared memory", hidden);
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    const int write_x = rows ? 0 : 1;
-    cudaError_t e;
-    if (dtype == VAPI_F32) {
-        auto kern = hyper_read_norm_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = launch(kern, n_out, threads, smem, stream, x, (const float*)y, mix, write, read, w, eps, kind, rows, (float*)out,
-                   n_out, hidden, streams, write_x);
-    } else if (dtype == VAPI_BF16) {
-        auto kern = hyper_read_norm_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = launch(kern, n_out, threads, smem, stream, x, (const __nv_bfloat16*)y, mix, write, read, w, eps, kind, rows,
-                   (__nv_bfloat16*)out, n_out, hidden, streams, write_x);
-    } else {
-        return fail(-2, "hyper_read_norm: unsupported dtype %d", dtype);
-    }
-    return check_launch("hyper_read_norm", e);
+    HyperArgs p;
+    p.mix = mix; p.write = write; p.read = read; p.w = w; p.eps = eps; p.kind = kind;
+    p.wy = wy; p.wy2 = wy2; p.eps_y = eps_y; p.y_scale = y_scale;
+    p.rows = rows; p.n_out = n_out; p.hidden = hidden; p.streams = streams; p.write_x = rows ? 0 : 1;
+    if (dtype == VAPI_F32) return launch_hyper<float>(x, y, y2, p, out, stream);
+    if (dtype == VAPI_BF16) return launch_hyper<__nv_bfloat16>(x, y, y2, p, out, stream);
+    return fail(-2, "hyper_read_norm: unsupported dtype %d", dtype);
 }
 
 // out[t, :] = scale * sum_b rmsnorm(a_b[t, :]) * w_b  for up to four branches: what mixers that run side by

@@ -16,17 +16,31 @@
 // W_down[e] hid[pos] in float; the sum over a token's pairs, its identity experts and the shared expert
 // is taken in a fixed order.
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 using namespace vapi;
 
 constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
+
+template <typename T> struct RtLd4;
+template <> struct RtLd4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct RtLd4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
 
 // One warp per token.  shared memory: per warp 2 * outputs floats (s and the choice scores) + groups floats.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ ranks,
                                  int* __restrict__ counts, int n, int width, int outputs, int experts, int top, int groups,
-                                 int keep) {
+                                 int keep, int vec4) {
     extern __shared__ float rt_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -37,12 +51,38 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     pdl_wait();
     if (t >= n) return;
     const T* hr = h + (size_t)t * width;
-    for (int e = 0; e < outputs; ++e) {
-        const float* w = wr + (size_t)e * width;
-        float acc = 0.f;
-        for (int k = lane; k < width; k += 32) acc = fmaf(to_f32(hr[k]), w[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
+    // four outputs at a time, so that a lane has their loads in flight together; the order of a lane's
+    // additions and of the warp's reduction depends on nothing but the width
+    for (int e0 = 0; e0 < outputs; e0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* w0 = wr + (size_t)e0 * width;
+        if (vec4) {
+            for (int k = lane * 4; k < width; k += 128) {
+                const float4 hv = RtLd4<T>::load(hr + k);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (e0 + j < outputs) {
+                        const float4 wv = *reinterpret_cast<const float4*>(w0 + (size_t)j * width + k);
+                        acc[j] = fmaf(hv.x, wv.x, acc[j]);
+                        acc[j] = fmaf(hv.y, wv.y, acc[j]);
+                        acc[j] = fmaf(hv.z, wv.z, acc[j]);
+                        acc[j] = fmaf(hv.w, wv.w, acc[j]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < width; k += 32) {
+                const float hv = to_f32(hr[k]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (e0 + j < outputs) acc[j] = fmaf(hv, w0[(size_t)j * width + k], acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0 && e0 + j < outputs) s[e0 + j] = v;
+        }
     }
     __syncwarp();
     float mx = -INFINITY;
@@ -230,6 +270,75 @@ moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restr
     }
 }
 
+// The same tile on the tensor cores for bfloat16 (K a multiple of 8, rows 16-byte aligned): see mma_tile.cuh.
+template <int MODE>
+__global__ void __launch_bounds__(MT_THREADS)
+moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, const __nv_bfloat16* __restrict__ W,
+                       const int* __restrict__ plan, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                       const int* __restrict__ offsets, const int* __restrict__ pair_of, const float* __restrict__ wts,
+                       void* __restrict__ out, int N, int K, int top) {
+    extern __shared__ __align__(128) unsigned char moe_smem[];
+    __shared__ const __nv_bfloat16* a_rows[MT_BM];
+    __shared__ const __nv_bfloat16* w_rows[MT_BN];
+    __shared__ int s_dst[MT_BM];
+    const int tile = blockIdx.x;
+    const int c0 = blockIdx.y * MT_BN;
+    pdl_trigger();
+    pdl_wait();
+    if (tile >= plan[0]) return;
+    const int e = tile_expert[tile], row0 = tile_row0[tile];
+    const int rows = min(MT_BM, offsets[e + 1] - row0);
+    const __nv_bfloat16* We = W + (size_t)e * N * K;
+    if (threadIdx.x < MT_BM) {
+        const int r = threadIdx.x;
+        const __nv_bfloat16* ap = nullptr;
+        int dst = -1;
+        if (r < rows) {
+            const int pos = row0 + r;
+            const int pair = pair_of[pos];
+            ap = A + (size_t)(MODE == 0 ? pair / top : pos) * a_stride;
+            dst = MODE == 0 ? pos : pair;
+        }
+        a_rows[r] = ap;
+        s_dst[r] = dst;
+        w_rows[r] = c0 + r < N ? We + (size_t)(c0 + r) * K : nullptr;
+    }
+    __syncthreads();
+    float acc[2][4][4];
+    mma_tile_64x64(a_rows, w_rows, K, W, reinterpret_cast<__nv_bfloat16*>(moe_smem), acc);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int dst = s_dst[wm * 32 + mi * 16 + g + 8 * h];
+            if (dst < 0) continue;
+            const float gw = MODE == 1 ? wts[dst] : 1.f;
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+                const int c = c0 + wn * 32 + ni * 8 + 2 * t;
+                const float v0 = acc[mi][ni][2 * h], v1 = acc[mi][ni][2 * h + 1];
+                if (MODE == 0) {
+                    const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
+                    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)dst * N + c;
+                    if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(r0 * r0, r1 * r1);
+                    else {
+                        if (c < N) o[0] = __float2bfloat16_rn(r0 * r0);
+                        if (c + 1 < N) o[1] = __float2bfloat16_rn(r1 * r1);
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)dst * N + c;
+                    if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<float2*>(o) = make_float2(gw * v0, gw * v1);
+                    else {
+                        if (c < N) o[0] = gw * v0;
+                        if (c + 1 < N) o[1] = gw * v1;
+                    }
+                }
+            }
+        }
+}
+
 // out[t, :] = sum over the token's choices (an expert's row of y, or weight * h for an identity expert)
 // + shared[t, :] (when given), in the order of the choices.
 template <typename T>
@@ -289,12 +398,13 @@ VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const 
     const size_t smem = (size_t)warps * (2 * outputs + groups) * sizeof(float);
     if (smem > 48 * 1024) return fail(-1, "moe_route: %d router outputs are too many", outputs);
     const int blocks = (n + warps - 1) / warps;
+    const int vec4 = (width % 4 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)wr & 15) == 0) ? 1 : 0;
     if (dtype == VAPI_F32)
         e = launch(moe_route_kernel<float>, blocks, warps * 32, smem, stream, (const float*)h, wr, corr, ids, wts, ranks, counts,
-                   n, width, outputs, experts, top, groups, keep);
+                   n, width, outputs, experts, top, groups, keep, vec4);
     else if (dtype == VAPI_BF16)
         e = launch(moe_route_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream, (const __nv_bfloat16*)h, wr, corr, ids, wts,
-                   ranks, counts, n, width, outputs, experts, top, groups, keep);
+                   ranks, counts, n, width, outputs, experts, top, groups, keep, vec4);
     else
         return fail(-2, "moe_route: unsupported dtype %d", dtype);
     int rc = check_launch("moe_route", e);
@@ -317,6 +427,22 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
     dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return fail(-1, "moe_grouped: %d output features are too many", N);
     cudaError_t e;
+    if (dtype == VAPI_BF16 && K % 8 == 0 && a_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaError_t a0 = cudaFuncSetAttribute(moe_grouped_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MT_SMEM);
+            cudaError_t a1 = cudaFuncSetAttribute(moe_grouped_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MT_SMEM);
+            if (a0 != cudaSuccess || a1 != cudaSuccess) return fail(-101, "moe_grouped: cannot reserve %zu bytes of shared memory", MT_SMEM);
+            attr_set = true;
+        }
+        if (mode == 0)
+            e = launch(moe_grouped_mma_kernel<0>, grid, MT_THREADS, MT_SMEM, stream, (const __nv_bfloat16*)A, a_stride,
+                       (const __nv_bfloat16*)W, plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);
+        else
+            e = launch(moe_grouped_mma_kernel<1>, grid, MT_THREADS, MT_SMEM, stream, (const __nv_bfloat16*)A, a_stride,
+                       (const __nv_bfloat16*)W, plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);
+        return check_launch("moe_grouped (tensor cores)", e);
+    }
 #define MOE_GO(T, M)                                                                                                         \
     e = launch(moe_grouped_kernel<T, M>, grid, 256, 0, stream, (const T*)A, a_stride, (const T*)W, plan, tile_expert,         \
                tile_row0, offsets, pair_of, wts, out, N, K, top)

@@ -17,6 +17,7 @@
 // end value), the segments' carries are chained, and every warp scans its segment again from its
 // carry, writing the outputs.  A decode step is the same call with one token a sequence (one warp).
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 using namespace vapi;
 
@@ -27,6 +28,7 @@ __device__ __forceinline__ float rg_gelu_tanh(float z) {
 }
 
 constexpr int RG_TM = 64, RG_TN = 64, RG_TK = 16;
+constexpr int RG_UN = 8;                  // tokens whose loads a lane of the scan keeps in flight
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -101,9 +103,70 @@ rglru_gates_kernel(const T* __restrict__ u, long long u_stride, const T* __restr
     }
 }
 
+// The gates on the tensor cores, for bfloat16 inputs and matrices (their products are exact in float, and the sums
+// are float: nothing is rounded that the float kernel above does not round).  A block takes 64 tokens x 32
+// channels of one part: rows 0..31 of its weight tile are the channels' rows of Ra, rows 32..63 those of Ri, so
+// the two warps on the left hold r, the two on the right i, and they meet through shared memory.
+__global__ void __launch_bounds__(MT_THREADS)
+rglru_gates_mma_kernel(const __nv_bfloat16* __restrict__ u, long long u_stride, const __nv_bfloat16* __restrict__ wa,
+                       const float* __restrict__ ba, const __nv_bfloat16* __restrict__ wi, const float* __restrict__ bi,
+                       const float* __restrict__ lam, float decay_c, float* __restrict__ a_out, float* __restrict__ g_out, int n,
+                       int channels, int bs) {
+    extern __shared__ __align__(128) unsigned char rg_tile_smem[];
+    __shared__ const __nv_bfloat16* a_rows[MT_BM];
+    __shared__ const __nv_bfloat16* w_rows[MT_BN];
+    const int b = blockIdx.z;
+    const int t0 = blockIdx.x * MT_BM, c0 = blockIdx.y * 32;
+    pdl_trigger();
+    if (threadIdx.x < MT_BM) {
+        const int r = threadIdx.x;
+        a_rows[r] = t0 + r < n ? u + (size_t)(t0 + r) * u_stride + (size_t)b * bs : nullptr;
+        const int c = c0 + (r & 31);
+        const __nv_bfloat16* base = (r < 32 ? wa : wi) + (size_t)b * bs * bs;
+        w_rows[r] = c < bs ? base + (size_t)c * bs : nullptr;
+    }
+    pdl_wait();
+    __syncthreads();
+    float acc[2][4][4];
+    mma_tile_64x64(a_rows, w_rows, bs, wa, reinterpret_cast<__nv_bfloat16*>(rg_tile_smem), acc);
+    // both gates' sums go through shared memory, so that a warp then owns whole rows of 32 channels: its global
+    // reads and writes are whole lines, and a lane's channel (with its bias and decay parameter) never changes
+    float* sr = reinterpret_cast<float*>(rg_tile_smem);          // [64][33]: the recurrence gate's sums
+    float* si = sr + 64 * 33;                                    // [64][33]: the input gate's sums
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, t = lane & 3;
+    float* dst = wn == 0 ? sr : si;
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    dst[(wm * 32 + mi * 16 + g + 8 * h) * 33 + ni * 8 + 2 * t + e] = acc[mi][ni][2 * h + e];
+    __syncthreads();
+    const int cb = c0 + lane;
+    if (cb >= bs) return;
+    const int c = b * bs + cb;
+    const float bias_a = ba[c], bias_i = bi[c], sp = decay_c * rg_softplus(lam[c]);
+    for (int row = warp; row < MT_BM; row += MT_THREADS / 32) {
+        const int tok = t0 + row;
+        if (tok >= n) break;
+        const float r = rg_sigmoid(sr[row * 33 + lane] + bias_a);
+        const float ig = rg_sigmoid(si[row * 33 + lane] + bias_i);
+        const float log_a = -r * sp;
+        const float mult = sqrtf(fmaxf(-expm1f(2.f * log_a), 0.f));
+        const float uv = __bfloat162float(u[(size_t)tok * u_stride + c]);
+        a_out[(size_t)tok * channels + c] = expf(log_a);
+        g_out[(size_t)tok * channels + c] = mult * ig * uv;
+    }
+}
+
 // grid (sequences, channel groups of 32); block = warps x 32; see the head of the file.
 template <typename T>
-__global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ g, const T* __restrict__ y,
+__global__ void __launch_bounds__(1024)
+rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ g, const T* __restrict__ y,
                                   long long y_stride, float* __restrict__ state, long long slot_stride,
                                   const int* __restrict__ state_slots, const int* __restrict__ cu_q,
                                   const int* __restrict__ positions, T* __restrict__ out, int channels, int num_slots,
@@ -130,7 +193,21 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
     float P = 1.f, E = 0.f;
     if (warps > 1) {
         if (ok) {
-            for (int t = lo; t < hi; ++t) {
+            int t = lo;
+            for (; t + RG_UN <= hi; t += RG_UN) {          // the loads of several tokens in flight together
+                float av[RG_UN], gv[RG_UN];
+#pragma unroll
+                for (int k = 0; k < RG_UN; ++k) {
+                    av[k] = a[(size_t)(q0 + t + k) * channels + c];
+                    gv[k] = g[(size_t)(q0 + t + k) * channels + c];
+                }
+#pragma unroll
+                for (int k = 0; k < RG_UN; ++k) {
+                    E = fmaf(av[k], E, gv[k]);
+                    P *= av[k];
+                }
+            }
+            for (; t < hi; ++t) {
                 const float av = a[(size_t)(q0 + t) * channels + c];
                 E = fmaf(av, E, g[(size_t)(q0 + t) * channels + c]);
                 P *= av;
@@ -142,7 +219,23 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
     }
     for (int w = 0; w < warp; ++w) S = fmaf(rg_smem[(w * 2) * 32 + lane], S, rg_smem[(w * 2 + 1) * 32 + lane]);
     if (!ok) return;
-    for (int t = lo; t < hi; ++t) {
+    int t = lo;
+    for (; t + RG_UN <= hi; t += RG_UN) {
+        float av[RG_UN], gv[RG_UN], yv[RG_UN];
+#pragma unroll
+        for (int k = 0; k < RG_UN; ++k) {
+            const size_t row = (size_t)(q0 + t + k);
+            av[k] = a[row * channels + c];
+            gv[k] = g[row * channels + c];
+            yv[k] = to_f32(y[row * y_stride + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < RG_UN; ++k) {
+            S = fmaf(av[k], S, gv[k]);
+            out[(size_t)(q0 + t + k) * channels + c] = from_f32<T>(S * rg_gelu_tanh(yv[k]));
+        }
+    }
+    for (; t < hi; ++t) {
         const size_t row = (size_t)(q0 + t);
         S = fmaf(a[row * channels + c], S, g[row * channels + c]);
         out[row * channels + c] = from_f32<T>(S * rg_gelu_tanh(to_f32(y[row * y_stride + c])));
@@ -162,8 +255,8 @@ VAPI_EXPORT int vapi_rglru(const void* u, long long u_stride, const void* y, lon
     const int bs = channels / blocks;
     dim3 grid1((n + RG_TM - 1) / RG_TM, (bs + RG_TN - 1) / RG_TN, blocks);
     if (grid1.z > 65535 || grid1.y > 65535) return fail(-1, "rglru: too many parts");
-    int warps = (max_q + 15) / 16;
-    warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
+    int warps = (max_q + 31) / 32;
+    warps = warps < 1 ? 1 : (warps > 32 ? 32 : warps);
     dim3 grid2(num_seqs, (channels + 31) / 32);
     if (grid2.y > 65535) return fail(-1, "rglru: too many channels");
     const size_t smem = (size_t)warps * 2 * 32 * sizeof(float);
@@ -177,6 +270,17 @@ VAPI_EXPORT int vapi_rglru(const void* u, long long u_stride, const void* y, lon
                    (const float*)y, y_stride, state, slot_stride, state_slots, cu_q, positions, (float*)out, channels, num_slots,
                    status);
     } else if (dtype == VAPI_BF16) {
+        if (bs % 8 == 0 && u_stride % 8 == 0 && ((uintptr_t)u & 15) == 0 && ((uintptr_t)wa & 15) == 0 && ((uintptr_t)wi & 15) == 0) {
+            static bool attr_set = false;
+            if (!attr_set) {
+                if (cudaFuncSetAttribute(rglru_gates_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MT_SMEM) != cudaSuccess)
+                    return fail(-101, "rglru: cannot reserve %zu bytes of shared memory", MT_SMEM);
+                attr_set = true;
+            }
+            dim3 grid_tc((n + MT_BM - 1) / MT_BM, (bs + 31) / 32, blocks);
+            e = launch(rglru_gates_mma_kernel, grid_tc, MT_THREADS, MT_SMEM, stream, (const __nv_bfloat16*)u, u_stride,
+                       (const __nv_bfloat16*)wa, ba, (const __nv_bfloat16*)wi, bi, lam, decay_c, a_buf, g_buf, n, channels, bs);
+        } else
         e = launch(rglru_gates_kernel<__nv_bfloat16>, grid1, 256, 0, stream, (const __nv_bfloat16*)u, u_stride,
                    (const __nv_bfloat16*)wa, ba, (const __nv_bfloat16*)wi, bi, lam, decay_c, a_buf, g_buf, n, channels, bs);
         int rc = check_launch("rglru_gates", e);

@@ -153,7 +153,7 @@ def rapolix_plan(cfg: RapolixConfig) -> ModelPlan:
                            weight_suffix="", names={"q": "q", "k": "k", "v": "v", "o": "o", "gate": "g"})
         rec = RGLRUMixer(W, ri["width"], ri["blocks"], ri["conv"], decay_c=DECAY_C, weight_suffix="", bias_suffix=".b",
                          names={"y": "y", "x": "x", "conv": "conv", "a": "ra", "i": "ri", "lam": "lam", "o": "o"})
-        mixer = ParallelMixer(W, [("left.", attn), ("right.", rec)], eps, norm_name="out")
+        mixer = ParallelMixer(W, [("left.", attn), ("right.", rec)], eps, norm_name="out", deferred=True)
         ffn = ffn_norm = None
         if layer.mlp is not None:
             m = dict(layer.mlp)

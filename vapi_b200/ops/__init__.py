@@ -1321,9 +1321,11 @@ _NORM_KINDS = {"layer": 0, "rms": 1}
 
 def hyper_read_norm(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], write: Optional[torch.Tensor],
                     read: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                    rows: Optional[torch.Tensor] = None, kind: str = "layer") -> Optional[torch.Tensor]:
+                    rows: Optional[torch.Tensor] = None, kind: str = "layer", branch=None) -> Optional[torch.Tensor]:
     """On the float32 streams ``x`` [n, S, H]: first the pending write of a sublayer's output ``y`` [n, H]
-    (``x_t <- sum_s mix[s, t] x_s + write[t] y`` for all t at once; ``y`` None: nothing pending), then
+    (``x_t <- sum_s mix[s, t] x_s + write[t] y`` for all t at once; ``y`` None: nothing pending; with
+    ``branch`` = ``(y2 | None, w_y, w_y2 | None, eps, scale)`` what is written is
+    ``scale * (rmsnorm(y) * w_y + rmsnorm(y2) * w_y2)``, the mean of two mixers' normed outputs), then
     ``u = sum_s read[s] x_s`` (``read`` None: every copy counts once) and its norm with ``weight`` (``kind``
     "layer": ``(u - mean) / sqrt(var + eps) * w``; "rms": ``u / sqrt(mean u^2 + eps) * w``) in ``out_dtype``.
     With ``rows`` only those rows are produced and ``x`` is left untouched; ``weight`` None: only the streams
@@ -1346,10 +1348,24 @@ def hyper_read_norm(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[to
         raise KernelError(f"the read vector must have {S} elements")
     if weight is not None and weight.numel() != hidden:
         raise KernelError(f"norm weight has {weight.numel()} elements for rows of {hidden}")
+    y2 = wy = wy2 = None
+    eps_y, y_scale = 0.0, 1.0
+    if branch is not None:
+        if y is None:
+            raise KernelError("branch norms come with a pending output")
+        y2, wy, wy2, eps_y, y_scale = branch
+        _cuda(y2, wy, wy2)
+        _f32(wy, "branch norm weight")
+        _f32(wy2, "branch norm weight")
+        if wy is None or wy.numel() != hidden or (y2 is not None and (wy2 is None or wy2.numel() != hidden)):
+            raise KernelError(f"branch norm weights must have {hidden} elements")
+        if y2 is not None and (not y2.is_contiguous() or y2.shape != y.shape or y2.dtype != y.dtype):
+            raise KernelError("the second branch must have the first one's shape and dtype")
     n_out = rows.numel() if rows is not None else n
     out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if weight is not None else None
     lib = _lib("hyper")
-    _check(lib, lib.vapi_hyper_read_norm(_p(x), _p(y), _DT[out_dtype], _p(mix), _p(write), _p(read), _p(weight),
+    _check(lib, lib.vapi_hyper_read_norm(_p(x), _p(y), _p(y2), _DT[out_dtype], _p(wy), _p(wy2), ctypes.c_float(eps_y),
+                                         ctypes.c_float(y_scale), _p(mix), _p(write), _p(read), _p(weight),
                                          ctypes.c_float(eps), _NORM_KINDS[kind], _p(rows), _p(out), n_out, hidden, S,
                                          _stream()))
     return out

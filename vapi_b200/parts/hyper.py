@@ -9,6 +9,7 @@ import torch
 from .. import ops
 from .base import CacheView, FeedForward, Mixer, Norm, Part, TensorSpec
 from .block import register_block
+from .parallel import DeferredBranches
 
 
 @dataclass
@@ -20,6 +21,9 @@ class HyperPending:
     y: torch.Tensor
     mix: torch.Tensor          # [S, S] float32, indexed [from, to]
     write: torch.Tensor        # [S] float32
+    #: ``(y2 | None, w_y, w_y2 | None, eps, scale)``: what is written is ``scale * (rms(y) w_y + rms(y2) w_y2)``,
+    #: the outputs of mixers side by side whose norms and mean the reading kernel takes on
+    branch: Any = None
 
 
 class HyperBlock(Part):
@@ -88,11 +92,17 @@ class HyperBlock(Part):
             raise TypeError("a block over several streams takes a HyperPending from the block before it")
         y, mix, write = (pending.y, pending.mix, pending.write) if pending is not None else (None, None, None)
         return ops.hyper_read_norm(x, y, mix, write, self.hc[key]["read"], norm.weight, norm.eps, ctx.dtype, None,
-                                   norm.kind)
+                                   norm.kind, pending.branch if pending is not None else None)
 
     def forward(self, x: torch.Tensor, delta: Optional[HyperPending], ctx: Any, cache: CacheView) -> HyperPending:
         a = self._read("mixer", self.mixer_norm, x, delta, ctx)
-        pending = HyperPending(self.mixer.forward(a, ctx, cache), self.hc["mixer"]["mix"], self.hc["mixer"]["write"])
+        y = self.mixer.forward(a, ctx, cache)
+        branch = None
+        if isinstance(y, DeferredBranches):          # mixers side by side: their norms and mean ride on the next read
+            branch = (y.outs[1] if len(y.outs) > 1 else None, y.weights[0], y.weights[1] if len(y.outs) > 1 else None,
+                      y.eps, y.scale)
+            y = y.outs[0]
+        pending = HyperPending(y, self.hc["mixer"]["mix"], self.hc["mixer"]["write"], branch)
         if self.ffn is None:
             return pending
         f = self._read("ffn", self.ffn_norm, x, pending, ctx)

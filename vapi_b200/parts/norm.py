@@ -68,11 +68,12 @@ class LayerNorm(Norm):
             y = delta.y if isinstance(delta, HyperPending) else delta
             return ops.hyper_read_norm(x.unsqueeze(1), y, self._one if y is not None else None,
                                        self._one if y is not None else None, None, self.weight, self.eps, dtype, rows,
-                                       self.kind)
+                                       self.kind, delta.branch if isinstance(delta, HyperPending) else None)
         if delta is not None and not isinstance(delta, HyperPending):
             raise TypeError("several streams take a sublayer's output with its mix matrix and write vector")
         y, mix, write = (delta.y, delta.mix, delta.write) if delta is not None else (None, None, None)
-        return ops.hyper_read_norm(x, y, mix, write, None, self.weight, self.eps, dtype, rows, self.kind)
+        return ops.hyper_read_norm(x, y, mix, write, None, self.weight, self.eps, dtype, rows, self.kind,
+                                   delta.branch if delta is not None else None)
 
 
 register_norm("rmsnorm", RMSNorm)
