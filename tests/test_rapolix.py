@@ -260,7 +260,8 @@ def test_the_router_and_the_experts(dtype):
     g = torch.Generator().manual_seed(9)
     tol = 3e-5 if dtype == torch.float32 else 3e-2
     for W, ff, E, I, top, groups, keep, n in ((48, 20, 6, 2, 2, 4, 2, 150), (64, 36, 5, 0, 1, 1, 1, 70), (40, 8, 9, 3, 4, 3, 2, 1),
-                                              (32, 16, 0, 2, 1, 1, 1, 5), (72, 100, 70, 2, 6, 9, 4, 300)):
+                                              (32, 16, 0, 2, 1, 1, 1, 5), (72, 100, 70, 2, 6, 9, 4, 300),
+                                              (64, 200, 4, 0, 2, 1, 1, 700), (136, 72, 3, 1, 2, 2, 1, 900)):
         h = torch.randn((n, W), generator=g).to(dtype)
         router = torch.randn((E + I, W), generator=g) * 0.6
         corr = torch.randn(E + I, generator=g) * 0.05

@@ -433,9 +433,37 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ y, const T* __restrict
     out[i] = from_f32<T>(to_f32(y[i]) * (1.f / (1.f + expf(-gv))));
 }
 
+// 16 bytes a thread (width and the gate's row stride multiples of 8, pointers 16-byte aligned)
+__global__ void sigmoid_gate_bf16x8_kernel(const uint4* __restrict__ y, const __nv_bfloat16* __restrict__ g, long long g_stride,
+                                           uint4* __restrict__ out, long long total8, int width8) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= total8) return;
+    const long long t = i / width8;
+    const int c8 = (int)(i - t * width8);
+    uint4 yv = y[i];
+    const uint4 gv = *reinterpret_cast<const uint4*>(g + (size_t)t * g_stride + (size_t)c8 * 8);
+    unsigned* yw = reinterpret_cast<unsigned*>(&yv);
+    const unsigned* gw = reinterpret_cast<const unsigned*>(&gv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&yw[k]));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+        __nv_bfloat162 r = __floats2bfloat162_rn(a.x * (1.f / (1.f + expf(-b.x))), a.y * (1.f / (1.f + expf(-b.y))));
+        yw[k] = *reinterpret_cast<unsigned*>(&r);
+    }
+    out[i] = yv;
+}
+
 VAPI_EXPORT int vapi_sigmoid_gate(const void* y, const void* g, long long g_stride, int dtype, void* out, int n, int width,
                                   cudaStream_t stream) {
     if (n <= 0 || width <= 0) return 0;
+    if (dtype == VAPI_BF16 && width % 8 == 0 && g_stride % 8 == 0 && (((uintptr_t)y | (uintptr_t)g | (uintptr_t)out) & 15) == 0) {
+        const long long total8 = (long long)n * (width / 8);
+        return check_launch("sigmoid_gate", launch(sigmoid_gate_bf16x8_kernel, (int)((total8 + 255) / 256), 256, 0, stream,
+                                                   (const uint4*)y, (const __nv_bfloat16*)g, g_stride, (uint4*)out, total8, width / 8));
+    }
     const long long total = (long long)n * width;
     const int blocks = (int)((total + 255) / 256);
     cudaError_t e;

@@ -8,10 +8,10 @@
 // lower index); their weights are their s divided by the sum of the chosen s (+ 1e-20).  An output
 // index >= experts is an identity expert: its output is the input itself.
 //
-// The step's expert work is laid out without the host learning anything about it: the router counts
-// the tokens of each expert and gives every (token, choice) pair its rank within its expert; one block
-// then turns the counts into offsets, lists the pairs expert by expert and cuts each expert's list into
-// tiles of 64 rows.  The two products launch enough blocks for the worst case; a block whose tile does
+// The step's expert work is laid out without the host learning anything about it: after the router, one
+// block counts the (token, choice) pairs of each expert in shared memory (a pair's rank within its expert is
+// the count it met), turns the counts into offsets, lists the pairs expert by expert and cuts each expert's
+// list into tiles of 64 rows.  The two products launch enough blocks for the worst case; a block whose tile does
 // not exist returns at once.  up: hid[pos] = relu(W_up[e] h[token])^2; down: y[pair] = weight *
 // W_down[e] hid[pos] in float; the sum over a token's pairs, its identity experts and the shared expert
 // is taken in a fixed order.
@@ -21,6 +21,10 @@
 using namespace vapi;
 
 constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
+
+// Rows of a tile of the experts' products: 128 when an expert's share of the step's pairs fills such tiles (a
+// prompt), else 64.  The plan and both products of a step must agree on it, so it depends on these two numbers only.
+static inline int moe_tile_rows(int pairs, int experts) { return experts > 0 && pairs / experts >= 192 ? 128 : 64; }
 
 template <typename T> struct RtLd4;
 template <> struct RtLd4<float> {
@@ -35,25 +39,26 @@ template <> struct RtLd4<__nv_bfloat16> {
     }
 };
 
-// One warp per token.  shared memory: per warp 2 * outputs floats (s and the choice scores) + groups floats.
+// One block of four warps per token: the warps share the router's outputs among them (four outputs at a time
+// a warp, so that a lane has their loads in flight together), then the first warp chooses.  The order of a
+// lane's additions and of a warp's reduction depends on nothing but the width.  shared memory: 2 * outputs
+// floats (the scores and the choice scores) + groups floats.
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
-                                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ ranks,
-                                 int* __restrict__ counts, int n, int width, int outputs, int experts, int top, int groups,
-                                 int keep, int vec4) {
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
+                 int* __restrict__ ids, float* __restrict__ wts, int n, int width, int outputs, int experts, int top,
+                 int groups, int keep, int vec4) {
     extern __shared__ float rt_smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    float* s = rt_smem + (size_t)warp * (2 * outputs + groups);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    float* s = rt_smem;
     float* choice = s + outputs;
     float* gscore = choice + outputs;
     pdl_trigger();
     pdl_wait();
     if (t >= n) return;
     const T* hr = h + (size_t)t * width;
-    // four outputs at a time, so that a lane has their loads in flight together; the order of a lane's
-    // additions and of the warp's reduction depends on nothing but the width
-    for (int e0 = 0; e0 < outputs; e0 += 4) {
+    for (int e0 = warp * 4; e0 < outputs; e0 += warps * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const float* w0 = wr + (size_t)e0 * width;
         if (vec4) {
@@ -84,6 +89,10 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
             if (lane == 0 && e0 + j < outputs) s[e0 + j] = v;
         }
     }
+    __syncthreads();
+    if (warp != 0) return;
+    {
+
     __syncwarp();
     float mx = -INFINITY;
     for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, s[e]);
@@ -146,7 +155,6 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         if (lane == 0) {
             ids[(size_t)t * top + r] = bi;
             wts[(size_t)t * top + r] = p;
-            ranks[(size_t)t * top + r] = bi < experts ? atomicAdd(counts + bi, 1) : -1;
             choice[bi] = NAN;                      // taken
         }
         __syncwarp();
@@ -155,36 +163,48 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         const float inv = 1.f / (total + 1e-20f);
         for (int r = 0; r < top; ++r) wts[(size_t)t * top + r] *= inv;
     }
+    __syncwarp();
+    }
 }
 
-// One block: counts -> offsets; the pairs expert by expert; the tiles.  plan[0] = number of tiles.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, const int* __restrict__ ranks, const int* __restrict__ counts,
-                                int* __restrict__ offsets, int* __restrict__ pair_of, int* __restrict__ plan,
-                                int* __restrict__ tile_expert, int* __restrict__ tile_row0, int pairs, int experts) {
-    extern __shared__ int pl_off[];            // [experts + 1]
+// One block: the pairs counted per expert (a pair's rank within its expert comes from the count, in shared
+// memory), counts -> offsets, the pairs listed expert by expert, the tiles.  plan[0] = number of tiles.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int* __restrict__ ranks, int* __restrict__ offsets,
+                                int* __restrict__ pair_of, int* __restrict__ plan, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int pairs, int experts, int tile_m) {
+    extern __shared__ int pl_smem[];           // counts [experts], offsets [experts + 1]
+    int* cnt = pl_smem;
+    int* off = pl_smem + experts;
     pdl_trigger();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
     pdl_wait();
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e < experts) ranks[p] = atomicAdd(cnt + e, 1);
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
-            pl_off[e] = acc;
+            off[e] = acc;
             offsets[e] = acc;
-            const int c = counts[e];
-            for (int r = 0; r < c; r += MOE_TM) {
+            const int c = cnt[e];
+            for (int r = 0; r < c; r += tile_m) {
                 tile_expert[tiles] = e;
                 tile_row0[tiles] = acc + r;
                 ++tiles;
             }
             acc += c;
         }
-        pl_off[experts] = acc;
+        off[experts] = acc;
         offsets[experts] = acc;
         plan[0] = tiles;
     }
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = ids[p];
-        if (e < experts) pair_of[pl_off[e] + ranks[p]] = p;
+        if (e < experts) pair_of[off[e] + ranks[p]] = p;
     }
 }
 
@@ -271,26 +291,27 @@ moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restr
 }
 
 // The same tile on the tensor cores for bfloat16 (K a multiple of 8, rows 16-byte aligned): see mma_tile.cuh.
-template <int MODE>
-__global__ void __launch_bounds__(MT_THREADS)
+template <int MODE, int BM, int BN, int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32)
 moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, const __nv_bfloat16* __restrict__ W,
                        const int* __restrict__ plan, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const int* __restrict__ offsets, const int* __restrict__ pair_of, const float* __restrict__ wts,
                        void* __restrict__ out, int N, int K, int top) {
     extern __shared__ __align__(128) unsigned char moe_smem[];
-    __shared__ const __nv_bfloat16* a_rows[MT_BM];
-    __shared__ const __nv_bfloat16* w_rows[MT_BN];
-    __shared__ int s_dst[MT_BM];
+    using Tile = MmaTile<BM, BN, WM, WN>;
+    __shared__ const __nv_bfloat16* a_rows[BM];
+    __shared__ const __nv_bfloat16* w_rows[BN];
+    __shared__ int s_dst[BM];
     const int tile = blockIdx.x;
-    const int c0 = blockIdx.y * MT_BN;
+    const int c0 = blockIdx.y * BN;
     pdl_trigger();
     pdl_wait();
     if (tile >= plan[0]) return;
     const int e = tile_expert[tile], row0 = tile_row0[tile];
-    const int rows = min(MT_BM, offsets[e + 1] - row0);
+    const int rows = min(BM, offsets[e + 1] - row0);
     const __nv_bfloat16* We = W + (size_t)e * N * K;
-    if (threadIdx.x < MT_BM) {
-        const int r = threadIdx.x;
+    for (int r = threadIdx.x; r < BN; r += Tile::THREADS) w_rows[r] = c0 + r < N ? We + (size_t)(c0 + r) * K : nullptr;
+    for (int r = threadIdx.x; r < BM; r += Tile::THREADS) {
         const __nv_bfloat16* ap = nullptr;
         int dst = -1;
         if (r < rows) {
@@ -301,23 +322,22 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, 
         }
         a_rows[r] = ap;
         s_dst[r] = dst;
-        w_rows[r] = c0 + r < N ? We + (size_t)(c0 + r) * K : nullptr;
     }
     __syncthreads();
-    float acc[2][4][4];
-    mma_tile_64x64(a_rows, w_rows, K, W, reinterpret_cast<__nv_bfloat16*>(moe_smem), acc);
+    float acc[Tile::MI][Tile::NI][4];
+    Tile::run(a_rows, w_rows, K, W, reinterpret_cast<__nv_bfloat16*>(moe_smem), acc);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, t = lane & 3;
+    const int wm = warp / WN, wn = warp % WN, g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int mi = 0; mi < 2; ++mi)
+    for (int mi = 0; mi < Tile::MI; ++mi)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int dst = s_dst[wm * 32 + mi * 16 + g + 8 * h];
+            const int dst = s_dst[wm * (BM / WM) + mi * 16 + g + 8 * h];
             if (dst < 0) continue;
             const float gw = MODE == 1 ? wts[dst] : 1.f;
 #pragma unroll
-            for (int ni = 0; ni < 4; ++ni) {
-                const int c = c0 + wn * 32 + ni * 8 + 2 * t;
+            for (int ni = 0; ni < Tile::NI; ++ni) {
+                const int c = c0 + wn * (BN / WN) + ni * 8 + 2 * t;
                 const float v0 = acc[mi][ni][2 * h], v1 = acc[mi][ni][2 * h + 1];
                 if (MODE == 0) {
                     const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
@@ -370,8 +390,29 @@ __global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ out
     out[i] = from_f32<T>(r * r);
 }
 
+// 16 bytes a thread (total a multiple of 8, both pointers 16-byte aligned)
+__global__ void relu_squared_bf16x8_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, long long total8) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (i >= total8) return;
+    uint4 v = x[i];
+    unsigned* w = reinterpret_cast<unsigned*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[k]));
+        f.x = fmaxf(f.x, 0.f); f.y = fmaxf(f.y, 0.f);
+        __nv_bfloat162 r = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+        w[k] = *reinterpret_cast<unsigned*>(&r);
+    }
+    out[i] = v;
+}
+
 VAPI_EXPORT int vapi_relu_squared(const void* x, void* out, int dtype, long long total, cudaStream_t stream) {
     if (total <= 0) return 0;
+    if (dtype == VAPI_BF16 && total % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0)
+        return check_launch("relu_squared", launch(relu_squared_bf16x8_kernel, (int)((total / 8 + 255) / 256), 256, 0, stream,
+                                                   (const uint4*)x, (uint4*)out, total / 8));
     const int blocks = (int)((total + 255) / 256);
     cudaError_t e;
     if (dtype == VAPI_F32) e = launch(relu_squared_kernel<float>, blocks, 256, 0, stream, (const float*)x, (float*)out, total);
@@ -381,7 +422,7 @@ VAPI_EXPORT int vapi_relu_squared(const void* x, void* out, int dtype, long long
     return check_launch("relu_squared", e);
 }
 
-// ids, wts, ranks: [n, top]; counts: [experts] (cleared here); offsets: [experts + 1]; pair_of: [n * top];
+// ids, wts, ranks: [n, top]; counts: [experts] (unused scratch); offsets: [experts + 1]; pair_of: [n * top];
 // plan: [1]; tile_expert, tile_row0: [max_tiles] with max_tiles >= n * top / 64 + experts.
 VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const float* corr, int* ids, float* wts, int* ranks,
                                int* counts, int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
@@ -392,27 +433,24 @@ VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const 
     if (groups < 1 || outputs % groups || keep < 1 || keep > groups)
         return fail(-1, "moe_route: %d outputs in %d groups, %d kept", outputs, groups, keep);
     if ((long long)(outputs / groups) * keep < top) return fail(-1, "moe_route: %d kept groups cannot give %d choices", keep, top);
-    cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)(experts > 0 ? experts : 1), stream);
-    if (e != cudaSuccess) return fail(-100, "moe_route: memset failed: %s", cudaGetErrorString(e));
-    const int warps = 4;
-    const size_t smem = (size_t)warps * (2 * outputs + groups) * sizeof(float);
+    cudaError_t e;
+    const size_t smem = (size_t)(2 * outputs + groups) * sizeof(float);
     if (smem > 48 * 1024) return fail(-1, "moe_route: %d router outputs are too many", outputs);
-    const int blocks = (n + warps - 1) / warps;
     const int vec4 = (width % 4 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)wr & 15) == 0) ? 1 : 0;
     if (dtype == VAPI_F32)
-        e = launch(moe_route_kernel<float>, blocks, warps * 32, smem, stream, (const float*)h, wr, corr, ids, wts, ranks, counts,
-                   n, width, outputs, experts, top, groups, keep, vec4);
+        e = launch(moe_route_kernel<float>, n, 128, smem, stream, (const float*)h, wr, corr, ids, wts, n, width, outputs,
+                   experts, top, groups, keep, vec4);
     else if (dtype == VAPI_BF16)
-        e = launch(moe_route_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream, (const __nv_bfloat16*)h, wr, corr, ids, wts,
-                   ranks, counts, n, width, outputs, experts, top, groups, keep, vec4);
+        e = launch(moe_route_kernel<__nv_bfloat16>, n, 128, smem, stream, (const __nv_bfloat16*)h, wr, corr, ids, wts, n,
+                   width, outputs, experts, top, groups, keep, vec4);
     else
         return fail(-2, "moe_route: unsupported dtype %d", dtype);
     int rc = check_launch("moe_route", e);
     if (rc != 0 || experts == 0) return rc;
-    const size_t psm = sizeof(int) * (size_t)(experts + 1);
+    const size_t psm = sizeof(int) * (size_t)(2 * experts + 1);
     if (psm > 48 * 1024) return fail(-1, "moe_route: %d experts are too many", experts);
-    e = launch(moe_plan_kernel, 1, 1024, psm, stream, (const int*)ids, (const int*)ranks, (const int*)counts, offsets, pair_of,
-               plan, tile_expert, tile_row0, n * top, experts);
+    e = launch(moe_plan_kernel, 1, 1024, psm, stream, (const int*)ids, ranks, offsets, pair_of, plan, tile_expert, tile_row0,
+               n * top, experts, moe_tile_rows(n * top, experts));
     return check_launch("moe_plan", e);
 }
 
@@ -427,22 +465,28 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
     dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return fail(-1, "moe_grouped: %d output features are too many", N);
     cudaError_t e;
+    const int tile_m = moe_tile_rows(pairs, experts);
     if (dtype == VAPI_BF16 && K % 8 == 0 && a_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaError_t a0 = cudaFuncSetAttribute(moe_grouped_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MT_SMEM);
-            cudaError_t a1 = cudaFuncSetAttribute(moe_grouped_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MT_SMEM);
-            if (a0 != cudaSuccess || a1 != cudaSuccess) return fail(-101, "moe_grouped: cannot reserve %zu bytes of shared memory", MT_SMEM);
-            attr_set = true;
-        }
-        if (mode == 0)
-            e = launch(moe_grouped_mma_kernel<0>, grid, MT_THREADS, MT_SMEM, stream, (const __nv_bfloat16*)A, a_stride,
-                       (const __nv_bfloat16*)W, plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);
-        else
-            e = launch(moe_grouped_mma_kernel<1>, grid, MT_THREADS, MT_SMEM, stream, (const __nv_bfloat16*)A, a_stride,
-                       (const __nv_bfloat16*)W, plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);
+#define MOE_TC(M, BM_, BN_, WM_, WN_)                                                                                        \
+    do {                                                                                                                     \
+        using Tile = MmaTile<BM_, BN_, WM_, WN_>;                                                                            \
+        auto kern = moe_grouped_mma_kernel<M, BM_, BN_, WM_, WN_>;                                                           \
+        static bool attr_set = false;                                                                                        \
+        if (!attr_set) {                                                                                                     \
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile::SMEM) != cudaSuccess)     \
+                return fail(-101, "moe_grouped: cannot reserve %zu bytes of shared memory", Tile::SMEM);                     \
+            attr_set = true;                                                                                                 \
+        }                                                                                                                    \
+        dim3 g(pairs / BM_ + experts, (N + BN_ - 1) / BN_);                                                                  \
+        e = launch(kern, g, Tile::THREADS, Tile::SMEM, stream, (const __nv_bfloat16*)A, a_stride, (const __nv_bfloat16*)W,   \
+                   plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);                                     \
+    } while (0)
+        if (tile_m == 128) { if (mode == 0) MOE_TC(0, 128, 128, 2, 4); else MOE_TC(1, 128, 128, 2, 4); }
+        else               { if (mode == 0) MOE_TC(0, 64, 64, 2, 2); else MOE_TC(1, 64, 64, 2, 2); }
+#undef MOE_TC
         return check_launch("moe_grouped (tensor cores)", e);
     }
+    if (tile_m != MOE_TM) return fail(-1, "moe_grouped: the float kernel has tiles of %d rows", MOE_TM);
 #define MOE_GO(T, M)                                                                                                         \
     e = launch(moe_grouped_kernel<T, M>, grid, 256, 0, stream, (const T*)A, a_stride, (const T*)W, plan, tile_expert,         \
                tile_row0, offsets, pair_of, wts, out, N, K, top)
