@@ -73,6 +73,16 @@ SERVING_HEADS = config([layer(left(heads=4, kv_heads=2, dim=64, vdim=64, scale=0
                               moe(ff=64, experts=8, identity=0, top=3, count=2, keep=1, shared=64))], width=128, streams=2)
 
 
+#: sizes that fit no vector width: a model width of 100, five streams, heads of 12 and 20, a window of one token, a
+#: window shorter than the kept count, parts of 10 channels, seven experts that are all chosen, an odd vocabulary
+ODD = config([layer(left(heads=5, kv_heads=5, dim=12, vdim=20, scale=0.4, size=1, keep_first=0), right(width=50, blocks=5, conv=1),
+                    moe(ff=10, experts=7, identity=0, top=7, count=None, shared=6)),
+              layer(left(heads=6, kv_heads=2, dim=20, vdim=12, scale=0.2, size=3, keep_first=30), right(width=36, blocks=2, conv=8), dense(34)),
+              layer(left(heads=1, kv_heads=1, dim=4, vdim=4, scale=1.0, size=200, keep_first=1), right(width=4, blocks=4, conv=2),
+                    moe(ff=6, experts=2, identity=4, top=3, count=3, keep=2, shared=None))],
+             width=100, vocab=133, streams=5, softcap=7.5, eps=1e-6)
+
+
 def write_model(folder: str, cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.12) -> str:
     """A model folder whose small parameters are far from their neutral values: slow and unlike decays, gate
     matrices that make the gates move, corrections of both signs, stream matrices that are no identity."""

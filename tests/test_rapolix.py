@@ -30,7 +30,7 @@ def kernels(request, monkeypatch):
 def folders(tmp_path_factory):
     out = {}
     for name, cfg, seed in (("mixed", ru.MIXED, 1), ("tiny", ru.TINY, 2), ("one_stream", ru.ONE_STREAM, 3),
-                            ("single_learned", ru.SINGLE_LEARNED, 4), ("serving_heads", ru.SERVING_HEADS, 6)):
+                            ("single_learned", ru.SINGLE_LEARNED, 4), ("serving_heads", ru.SERVING_HEADS, 6), ("odd", ru.ODD, 7)):
         out[name] = ru.write_model(str(tmp_path_factory.mktemp(name)), cfg, seed)
         out[name + "/bf16"] = ru.write_model(str(tmp_path_factory.mktemp(name + "bf16")), cfg, seed, torch.bfloat16, std=0.05)
     return out
@@ -368,7 +368,8 @@ def test_windowed_attention_with_kept_tokens_against_its_restatement_in_a_mixed_
 @pytest.mark.parametrize("device,name,length", [pytest.param("cpu", "tiny", 24, id="host"),
                                                 pytest.param("cuda", "mixed", 140, marks=pytest.mark.gpu, id="gpu"),
                                                 pytest.param("cuda", "one_stream", 90, marks=pytest.mark.gpu, id="gpu-one-stream"),
-                                                pytest.param("cuda", "single_learned", 60, marks=pytest.mark.gpu, id="gpu-single-learned")])
+                                                pytest.param("cuda", "single_learned", 60, marks=pytest.mark.gpu, id="gpu-single-learned"),
+                                                pytest.param("cuda", "odd", 70, marks=pytest.mark.gpu, id="gpu-odd-sizes")])
 def test_whole_prompt_token_by_token_and_portions_agree_with_the_plain_model(device, name, length, folders, kernels):
     kernels(device)
     oracle = ru.Oracle(folders[name])
@@ -415,7 +416,7 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(device, name, 
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name,page", [("mixed", 16), ("serving_heads", 64)])
+@pytest.mark.parametrize("name,page", [("mixed", 16), ("serving_heads", 64), ("odd", 16)])
 def test_bfloat16_serving_path(name, page, folders, kernels):
     """(`serving_heads`: keys and values of 64 and of 128 on pages of 64 tokens, the shapes that the tensor-core
     attention kernels take; its windows end inside pages, and one layer keeps more first tokens than a page.)"""
