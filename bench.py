@@ -775,7 +775,7 @@ def rapolix_sizes(name):
     sparse = {"type": "parallel", "mixer": mixer, "mlp": {
         "kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
         "router": {"experts": 30, "identity": 2, "top": 4, "groups": {"count": 4, "keep": 2}}}}
-    rp = {"architecture": "Rapolix", "vocab": lf["vocab_size"], "width": W, "streams": 2, "logit_softcap": 30.0,
+    rp = {"architecture": "Rapolix", "vocab": lf["vocab_size"], "width": W, "streams": 2, "logit_softcap": 50.0,
           "norm": {"eps": 1e-5}, "layers": [dense, sparse] * 4}
     lf = dict(lf, num_hidden_layers=8, layer_types=["conv", "conv", "conv", "full_attention"] * 2)
     return rp, lf

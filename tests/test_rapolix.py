@@ -319,7 +319,7 @@ def test_a_planted_key_is_seen_inside_the_window_and_among_the_kept_first_tokens
     four warps, tcgen05 from 64 tokens on), everything else on the general kernel."""
     from vapi_b200 import ops
     klen = 420
-    for window, keep in ((72, 20), (64, 64), (100, 1), (33, 130), (50, 0)):
+    for window, keep in ((75, 21), (64, 64), (100, 1), (33, 130), (50, 0)):
         edge = klen - window                              # the last query's window starts right behind this key
         for j_star in sorted({0, keep - 1, keep, 63, 64, 127, 128, edge - qlen, edge, edge + 1, klen - qlen, klen - 1} & set(range(klen))):
             q, cache, table = _planted(klen, qlen, j_star, dk=dk, dv=dv, page=page, dtype=dtype)
@@ -356,7 +356,7 @@ def test_windowed_attention_with_kept_tokens_against_its_restatement_in_a_mixed_
     q = (torch.randn((n, nh * dk), generator=g) * 0.7).to(dtype)
     cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
     kl = torch.tensor(klens, dtype=torch.int32)
-    for window, keep in ((72, 20), (5, 7), (1000, 3), (64, 0)):
+    for window, keep in ((90, 17), (5, 7), (1000, 3), (64, 0)):
         want = plain_ops.masked_attention(q, q.stride(0), cache, page, table, cu, kl, n, S, max(lens), max(klens), nh, nkv, dk, dv,
                                           0.2, window=window, keep=keep)
         got = ops.masked_attention(q.cuda(), q.stride(0), cache.cuda(), page, table.cuda(), cu.cuda(), kl.cuda(), n, S, max(lens),
