@@ -423,10 +423,10 @@ VAPI_EXPORT int vapi_relu_squared(const void* x, void* out, int dtype, long long
     return check_launch("relu_squared", e);
 }
 
-// ids, wts, ranks: [n, top]; counts: [experts] (unused scratch); offsets: [experts + 1]; pair_of: [n * top];
+// ids, wts, ranks: [n, top]; offsets: [experts + 1]; pair_of: [n * top];
 // plan: [1]; tile_expert, tile_row0: [max_tiles] with max_tiles >= n * top / 64 + experts.
 VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const float* corr, int* ids, float* wts, int* ranks,
-                               int* counts, int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
+                               int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
                                int width, int outputs, int experts, int top, int groups, int keep, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (outputs <= 0 || experts < 0 || experts > outputs || top <= 0 || top > outputs)

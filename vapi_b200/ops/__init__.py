@@ -1488,17 +1488,17 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, e
     pairs = n * top
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     wts = torch.empty((n, top), dtype=torch.float32, device=dev)
-    # ranks | counts | offsets | pair_of | number of tiles | tile_expert | tile_row0, one allocation
+    # ranks | offsets | pair_of | number of tiles | tile_expert | tile_row0, one allocation
     max_tiles = pairs // 64 + max(experts, 1)
-    sizes = [pairs, max(experts, 1), experts + 1, pairs, 1, max_tiles, max_tiles]
+    sizes = [pairs, experts + 1, pairs, 1, max_tiles, max_tiles]
     book = torch.empty((sum(sizes),), dtype=torch.int32, device=dev)
     parts, at = [], 0
     for z in sizes:
         parts.append(book[at:at + z])
         at += z
-    ranks, counts, offsets, pair_of, ntiles, tile_expert, tile_row0 = parts
+    ranks, offsets, pair_of, ntiles, tile_expert, tile_row0 = parts
     lib = _lib("moe")
-    _check(lib, lib.vapi_moe_route(_p(h), _dt(h), _p(router), _p(correction), _p(ids), _p(wts), _p(ranks), _p(counts),
+    _check(lib, lib.vapi_moe_route(_p(h), _dt(h), _p(router), _p(correction), _p(ids), _p(wts), _p(ranks),
                                    _p(offsets), _p(pair_of), _p(ntiles), _p(tile_expert), _p(tile_row0), n, W, outputs,
                                    int(experts), int(top), int(groups), int(keep), _stream()), 2 if experts > 0 else 1)
     return ids, wts, (offsets, pair_of, ntiles, tile_expert, tile_row0)
